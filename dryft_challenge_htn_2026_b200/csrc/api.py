@@ -1,0 +1,280 @@
+"""Python entry points of the CUDA kernels: thin ctypes wrappers that take torch tensors.
+
+Every function launches on torch's current CUDA stream and returns without synchronising, so
+the calls can be captured in a CUDA graph. Arguments are checked here (device, dtype, contiguity,
+the sizes a kernel supports); a kernel that cannot take a size raises ``KernelError`` rather than
+compute something else. There is no CPU or library fallback behind these functions.
+"""
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+PAGE = 64  # tokens per cache page; must equal DK_PAGE in common.cuh
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_pdl = False
+
+
+def set_pdl(on):
+    """Programmatic dependent launch for every kernel launched from here on."""
+    global _pdl
+    _pdl = bool(on)
+    for lib in list(build._libs.values()):
+        lib.dk_set_pdl(int(_pdl))
+
+
+def _lib(source, defines=None):
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: the kernels of this library run on an NVIDIA B200 (sm_100a) only")
+    key = (source, tuple(sorted((defines or {}).items())))
+    fresh = key not in build._libs
+    lib = build.load_lib(source, defines)
+    if fresh:
+        lib.dk_set_pdl.argtypes = [c_int]
+        lib.dk_set_pdl(int(_pdl))
+        lib.dk_error_string.restype = ctypes.c_char_p
+    return lib
+
+
+def _check(lib, err, what):
+    if err != 0:
+        msg = lib.dk_error_string(err).decode()
+        raise KernelError(f"{what}: CUDA error {err} ({msg})")
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"unsupported dtype {t.dtype}: kernels take float32 or bfloat16")
+
+
+def _need(t, name, dtype=None, dim=None):
+    if t is None:
+        return
+    if not t.is_cuda or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} must have {dim} dimensions, got shape {tuple(t.shape)}")
+
+
+# ------------------------------------------------------------------------------------ row kernels
+def embed_rmsnorm(tok, embed, norm_w, eps, h_out, a_out):
+    """h_out[t] = embed[tok[t]] (float32); a_out[t] = rmsnorm(h_out[t]) * norm_w."""
+    _need(tok, "tok", torch.int32, 1), _need(embed, "embed", None, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(h_out, "h_out", torch.float32, 2), _need(a_out, "a_out", embed.dtype, 2)
+    lib = _lib("elementwise.cu")
+    n, (V, H) = tok.numel(), embed.shape
+    _check(lib, lib.dk_embed_rmsnorm(_dt(embed), _p(tok), _p(embed), _p(norm_w), c_float(eps), n, H, V, _p(h_out),
+                                     _p(a_out), _stream()), "embed_rmsnorm")
+
+
+def add_rmsnorm(h, delta, norm_w, eps, a_out, rows=None):
+    """h += delta (delta may be None); a_out = rmsnorm(h) * norm_w. With ``rows`` (int32 indices)
+    only those rows are normalised into a_out[0..len(rows)) and h is left unchanged."""
+    _need(h, "h", torch.float32, 2), _need(delta, "delta", a_out.dtype, 2), _need(norm_w, "norm_w", torch.float32, 1)
+    _need(rows, "rows", torch.int32, 1), _need(a_out, "a_out", None, 2)
+    lib = _lib("elementwise.cu")
+    n = h.shape[0] if rows is None else rows.numel()
+    _check(lib, lib.dk_add_rmsnorm(_dt(a_out), _p(h), _p(delta), _p(rows), _p(norm_w), c_float(eps), n, h.shape[1],
+                                   _p(a_out), _stream()), "add_rmsnorm")
+
+
+def silu_mul(gu, out):
+    """out[r, c] = silu(gu[r, c]) * gu[r, I + c] for gu [rows, 2I]."""
+    _need(gu, "gu", None, 2), _need(out, "out", gu.dtype, 2)
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_silu_mul(_dt(gu), _p(gu), _p(out), c_longlong(gu.shape[0]), out.shape[1], _stream()), "silu_mul")
+
+
+def gather_rows_f32(src, rows, out):
+    _need(src, "src", torch.float32, 2), _need(rows, "rows", torch.int32, 1), _need(out, "out", torch.float32, 2)
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_gather_rows_f32(_p(src), _p(rows), _p(out), rows.numel(), src.shape[1], _stream()), "gather_rows")
+
+
+def qk_norm_rope_write(qkv, q_out, q_norm_w, k_norm_w, cos, sin, row_pos, row_seq, page_table, k_store, v_store,
+                       n_heads, n_kv_heads, head_dim, eps, write_kv=True):
+    """Per-head RMSNorm (weights may be None), rotate-half rotation (cos/sin [positions, hd/2]
+    float32, may be None), q to q_out [T, nh*hd], k and v into the paged stores
+    [pages, n_kv, PAGE, hd] at each token's position. Rows with position < 0 are skipped."""
+    _need(qkv, "qkv", None, 2), _need(q_out, "q_out", qkv.dtype, 2)
+    _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
+    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", qkv.dtype), _need(v_store, "v_store", qkv.dtype)
+    if head_dim % 2 or head_dim > 256:
+        raise KernelError(f"head size {head_dim} not supported: even, at most 256")
+    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {qkv.shape[1]} != (nh + 2 nkv) * hd")
+    lib = _lib("elementwise.cu")
+    _check(lib, lib.dk_qk_norm_rope_write(_dt(qkv), _p(qkv), _p(q_out), _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin),
+                                          _p(row_pos), _p(row_seq), _p(page_table), page_table.shape[1], _p(k_store),
+                                          _p(v_store), qkv.shape[0], n_heads, n_kv_heads, head_dim, c_float(eps),
+                                          int(bool(write_kv)), _stream()), "qk_norm_rope_write")
+
+
+# -------------------------------------------------------------------------------------- attention
+def attention_generic(q, out, k_store, v_store, row_pos, row_seq, page_table, n_heads, n_kv_heads, head_dim, window,
+                      scale):
+    """Float32-arithmetic attention of every token row over its sequence's cached keys up to its
+    own position (window: keys a query sees, 0 = all). Any phase; float32 or bfloat16 storage."""
+    _need(q, "q", None, 2), _need(out, "out", q.dtype, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    if head_dim > 256 or n_heads % n_kv_heads:
+        raise KernelError(f"attention: head size {head_dim} (max 256) / heads {n_heads}:{n_kv_heads} not supported")
+    lib = _lib("attention_generic.cu")
+    _check(lib, lib.dk_attention_generic(_dt(q), _p(q), _p(out), _p(k_store), _p(v_store), _p(row_pos), _p(row_seq),
+                                         _p(page_table), page_table.shape[1], q.shape[0], n_heads, n_kv_heads,
+                                         head_dim, int(window or 0), c_float(scale), _stream()), "attention_generic")
+
+
+def _attn_lib(head_dim):
+    if head_dim % 16 or not 16 <= head_dim <= 256:
+        raise KernelError(f"bfloat16 attention: head size {head_dim} not supported (multiples of 16 up to 256)")
+    return _lib("attention_bf16.cu", {"HD": head_dim})
+
+
+def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads, n_kv_heads, head_dim,
+                           window, scale):
+    """Ragged causal attention of query chunks (tensor cores). tiles [n, 2] int32 = (sequence,
+    first query of a 64-row tile within its chunk); cu_q [nseq+1]; seq_pos0 [nseq] cached length
+    before the chunk."""
+    _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2), _need(tiles, "tiles", torch.int32, 2)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2)
+    if n_heads % n_kv_heads:
+        raise KernelError(f"attention: {n_heads} query heads are not a multiple of {n_kv_heads} kv heads")
+    lib = _attn_lib(head_dim)
+    _check(lib, lib.dk_attn_prefill_bf16(_p(q), _p(out), _p(k_store), _p(v_store), _p(tiles), tiles.shape[0], _p(cu_q),
+                                         _p(seq_pos0), _p(page_table), page_table.shape[1], n_heads, n_kv_heads,
+                                         int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
+
+
+def decode_splits(n_seq, n_kv_heads, group, max_splits=32, target_blocks=296):
+    """Number of key splits for decode attention: enough blocks to fill the GPU, fixed for a batch
+    size (it must not depend on sequence lengths, which change under a captured graph)."""
+    blocks = n_seq * n_kv_heads * ((group + 15) // 16)
+    n = 1
+    while n < max_splits and blocks * n < target_blocks:
+        n *= 2
+    return n
+
+
+def attention_decode_ws(n_seq, n_heads, head_dim, nsplit, device):
+    """Scratch for attention_decode_bf16: float32 partial outputs and (max, sum) pairs."""
+    if nsplit == 1:
+        return None, None
+    return (torch.empty(n_seq * n_heads * nsplit * head_dim, dtype=torch.float32, device=device),
+            torch.empty(n_seq * n_heads * nsplit * 2, dtype=torch.float32, device=device))
+
+
+def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads, head_dim, window, scale,
+                          nsplit, ws_acc=None, ws_ml=None):
+    """One query token per sequence over its cached keys [.., row_pos] (tensor cores, keys split
+    over ``nsplit`` blocks and merged)."""
+    _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
+    n_seq = q.shape[0]
+    if nsplit > 1:
+        _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
+        if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * nsplit * head_dim \
+                or ws_ml.numel() < n_seq * n_heads * nsplit * 2:
+            raise KernelError("attention_decode_bf16: scratch too small for this batch and split count")
+    lib = _attn_lib(head_dim)
+    _check(lib, lib.dk_attn_decode_bf16(_p(q), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos),
+                                        _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
+                                        int(window or 0), c_float(scale), nsplit, _stream()), "attention_decode_bf16")
+
+
+# ---------------------------------------------------------------------------------------- products
+MODE_STORE, MODE_STORE_F32, MODE_SILU = 0, 1, 2
+GEMV_MAX_ROWS = 64
+
+
+def sgemm(x, w, out, mode=MODE_STORE):
+    """float32 out = x . w^T on CUDA cores; mode MODE_SILU: w = [gate; up], out = silu(g) * u."""
+    _need(x, "x", torch.float32, 2), _need(w, "w", torch.float32, 2), _need(out, "out", torch.float32, 2)
+    M, K = x.shape
+    N = out.shape[1]
+    if w.shape != ((2 * N if mode == MODE_SILU else N), K) or out.shape[0] != M:
+        raise KernelError(f"sgemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
+    lib = _lib("gemm.cu")
+    _check(lib, lib.dk_sgemm(_p(x), _p(w), _p(out), M, N, K, mode, _stream()), "sgemm")
+
+
+def gemv_plan(M, N, K, mode):
+    """(R, KS): weight-row tiles and K slices per block. Enough blocks to cover the GPU's 148 SMs
+    about twice when the matrix allows it, and no more warps than the register file holds."""
+    max_warps = 16 if M <= 16 else 8
+    tiles = (N + 15) // 16
+    chunks = (K + 31) // 32
+    if mode == MODE_SILU:
+        ks = max_warps // 2
+        while ks > 1 and chunks < 8 * ks:
+            ks //= 2
+        return 2, ks
+    r = 1
+    while r < max_warps and tiles // (r * 2) >= 296:
+        r *= 2
+    ks = max_warps // r
+    while ks > 1 and chunks < 8 * ks:
+        ks //= 2
+    return r, ks
+
+
+def gemv_bf16(x, w, out, mode=MODE_STORE, plan=None):
+    """Skinny bfloat16 product for at most 64 rows of x; out bfloat16 (modes 0, 2) or float32 (1)."""
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
+    M, K = x.shape
+    N = out.shape[1]
+    if M > GEMV_MAX_ROWS or K % 8:
+        raise KernelError(f"gemv_bf16: {M} rows (max {GEMV_MAX_ROWS}) / inner size {K} (multiple of 8) not supported")
+    if w.shape != ((2 * N if mode == MODE_SILU else N), K) or out.shape[0] != M:
+        raise KernelError(f"gemv_bf16: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
+    if out.dtype != (torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16):
+        raise KernelError(f"gemv_bf16: out dtype {out.dtype} does not fit mode {mode}")
+    r, ks = plan or gemv_plan(M, N, K, mode)
+    lib = _lib("gemm.cu")
+    _check(lib, lib.dk_gemv_bf16(_p(x), _p(w), _p(out), M, N, K, mode, r, ks, _stream()), "gemv_bf16")
+
+
+# ---------------------------------------------------------------------------------------- sampling
+def sample_chunks(vocab):
+    return _lib("sampling.cu").dk_sample_chunks(vocab)
+
+
+def sample(logits, temperature, seeds, pos, rows, ws_val, ws_idx, out_tok, advance=False):
+    """out_tok[b] = argmax (temperature 0) or Gumbel-max draw of logits[b]. temperature [n]
+    float32, seeds [n, 2] int32 (low, high word of each row's 64-bit seed), pos int32 positions
+    indexed through ``rows`` (or directly when rows is None); the draw's counter is that position
+    + 1, the place the new token will take. ``advance`` moves those positions on by one."""
+    _need(logits, "logits", torch.float32, 2), _need(temperature, "temperature", torch.float32, 1)
+    _need(seeds, "seeds", torch.int32, 2), _need(pos, "pos", torch.int32, 1), _need(rows, "rows", torch.int32, 1)
+    _need(ws_val, "ws_val", torch.float32), _need(ws_idx, "ws_idx", torch.int32), _need(out_tok, "out_tok", torch.int32, 1)
+    n, V = logits.shape
+    lib = _lib("sampling.cu")
+    need = n * lib.dk_sample_chunks(V)
+    if ws_val.numel() < need or ws_idx.numel() < need:
+        raise KernelError("sample: scratch too small")
+    _check(lib, lib.dk_sample(_p(logits), n, V, _p(temperature), _p(seeds), _p(pos), _p(rows), _p(ws_val), _p(ws_idx),
+                              _p(out_tok), int(bool(advance)), _stream()), "sample")

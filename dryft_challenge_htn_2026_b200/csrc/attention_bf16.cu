@@ -1,0 +1,397 @@
+// bfloat16 causal grouped-query attention over the paged cache on the tensor cores
+// (mma.sync m16n8k16, float32 scores / softmax / accumulators). Built once per head size with
+// -DHD=<multiple of 16, at most 256>.
+//
+//  * prefill: ragged batch of query chunks; a block owns 64 consecutive queries of one sequence
+//    and one query head (4 warps x 16 rows) and walks the key pages up to its diagonal.
+//  * decode: one query token per sequence; a block owns the (up to 16) query heads that share a
+//    kv head and one split of the keys; its 4 warps take 16 keys each of every 64-key page and
+//    are merged through shared memory; splits are merged by the combine kernel.
+// Key/value pages ([64, HD] per kv head, contiguous) are staged in shared memory with cp.async,
+// two stages deep. P is rounded to bfloat16 before P.V; row sums use the unrounded values.
+// Reference formulas: engine/fused.py:301-343 (prefill), :478-565 (split decode + combine).
+#include "common.cuh"
+
+#ifndef HD
+#error "compile with -DHD=<head size>"
+#endif
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
+
+constexpr int KSTR = HD + 8;                      // shared-memory row stride (elements): 16 B of padding
+constexpr int TILE_ELEMS = DK_PAGE * KSTR;        // one staged K or V page
+constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;       // K then V
+constexpr size_t SMEM_BYTES = 2 * STAGE_ELEMS * sizeof(bf16);
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const bf16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void cp_async16(bf16* smem, const bf16* gmem) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// All threads of the block copy one page (K and V of kv head kvh) into a stage.
+__device__ __forceinline__ void stage_page(bf16* stage, const bf16* k_store, const bf16* v_store, int page, int nkv,
+                                           int kvh) {
+    const size_t off = kv_offset(page, nkv, kvh, 0, HD);
+    constexpr int CPR = HD / 8;  // 16-byte chunks per row
+    for (int c = threadIdx.x; c < DK_PAGE * CPR; c += blockDim.x) {
+        const int row = c / CPR, col = (c % CPR) * 8;
+        cp_async16(stage + row * KSTR + col, k_store + off + (size_t)row * HD + col);
+        cp_async16(stage + TILE_ELEMS + row * KSTR + col, v_store + off + (size_t)row * HD + col);
+    }
+}
+
+// Q fragments of 16 rows; row_ptr0/1: the rows of lane group g and g+8 (nullptr: row of zeros).
+__device__ __forceinline__ void load_q_frags(uint32_t (&qf)[HD / 16][4], const bf16* row0, const bf16* row1) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ks++) {
+        const int c = ks * 16 + 2 * t;
+        qf[ks][0] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c) : 0u;
+        qf[ks][1] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c) : 0u;
+        qf[ks][2] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c + 8) : 0u;
+        qf[ks][3] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c + 8) : 0u;
+    }
+}
+
+// One warp: 16 query rows against NKEYS staged keys (rows of Ks / Vs), online softmax update.
+// Row r (0: lane group g, 1: g+8) may see keys with lo[r] <= absolute position <= hi[r].
+// Scores are kept in the log2 domain: sl2 = scale * log2(e).
+template <int NKEYS>
+__device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], const bf16* Ks, const bf16* Vs, int key0,
+                                            const int (&lo)[2], const int (&hi)[2], float sl2, float (&m)[2],
+                                            float (&l)[2], float (&acc)[HD / 8][4]) {
+    const int lane = threadIdx.x & 31, t = lane & 3;
+    float s[NKEYS / 8][4];
+#pragma unroll
+    for (int i = 0; i < NKEYS / 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const int j = lane >> 3;
+#pragma unroll
+    for (int np = 0; np < NKEYS / 16; np++) {
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ks++) {
+            uint32_t b[4];
+            ldsm_x4(b, Ks + (np * 16 + (lane & 7) + 8 * (j >> 1)) * KSTR + ks * 16 + 8 * (j & 1));
+            mma16816(s[2 * np], qf[ks], b[0], b[1]);
+            mma16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NKEYS / 8; nt++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int key = key0 + nt * 8 + 2 * t + (c & 1), r = c >> 1;
+            const float v = (key >= lo[r] && key <= hi[r]) ? s[nt][c] * sl2 : -INFINITY;
+            s[nt][c] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float ms[2], alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float m_new = fmaxf(m[r], mx[r]);
+        ms[r] = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = exp2f(m[r] - ms[r]);
+        m[r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < NKEYS / 8; nt++) {
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float p = exp2f(s[nt][c] - ms[c >> 1]);
+            s[nt][c] = p;
+            sum[c >> 1] += p;
+        }
+    }
+    l[0] = l[0] * alpha[0] + sum[0];
+    l[1] = l[1] * alpha[1] + sum[1];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) {
+        acc[i][0] *= alpha[0];
+        acc[i][1] *= alpha[0];
+        acc[i][2] *= alpha[1];
+        acc[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kk = 0; kk < NKEYS / 16; kk++) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; dp++) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, Vs + (kk * 16 + (lane & 15)) * KSTR + dp * 16 + 8 * (lane >> 4));
+            mma16816(acc[2 * dp], a, b[0], b[1]);
+            mma16816(acc[2 * dp + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------- prefill
+// grid (tiles, nh). tiles[2i] = sequence, tiles[2i+1] = first query of the tile within the
+// sequence's chunk. cu_q: first flat row of each sequence's chunk; seq_pos0: tokens already cached
+// before the chunk (the chunk's own keys are in the cache when this runs).
+__global__ void __launch_bounds__(128)
+attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v_store, const int* tiles,
+                    const int* cu_q, const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv,
+                    int window, float sl2) {
+    extern __shared__ __align__(16) bf16 smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int q_len = cu_q[seq + 1] - cu_q[seq];
+    const int pos0 = seq_pos0[seq];
+    const int rows_here = min(64, q_len - q0);
+    const int* pt = page_table + (size_t)seq * pt_stride;
+
+    const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;  // rows within the chunk
+    const bool ok0 = r0 < q_len, ok1 = r1 < q_len;
+    const size_t flat0 = (size_t)(cu_q[seq] + r0), flat1 = (size_t)(cu_q[seq] + r1);
+    uint32_t qf[HD / 16][4];
+    load_q_frags(qf, ok0 ? q + (flat0 * nh + h) * HD : nullptr, ok1 ? q + (flat1 * nh + h) * HD : nullptr);
+    int lo[2], hi[2];
+    hi[0] = ok0 ? pos0 + r0 : -1;
+    hi[1] = ok1 ? pos0 + r1 : -1;
+    lo[0] = window > 0 ? max(0, hi[0] - window + 1) : 0;
+    lo[1] = window > 0 ? max(0, hi[1] - window + 1) : 0;
+    // keys this warp's 16 rows can see at all
+    const int w_first = pos0 + q0 + warp * 16;
+    const int w_hi = min(w_first + 15, pos0 + q_len - 1);
+    const int w_lo = window > 0 ? max(0, w_first - window + 1) : 0;
+
+    const int max_pos = pos0 + q0 + rows_here - 1;
+    const int min_pos = pos0 + q0;
+    const int jt_hi = max_pos / DK_PAGE;
+    const int jt_lo = window > 0 ? max(0, min_pos - window + 1) / DK_PAGE : 0;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    stage_page(smem, k_store, v_store, pt[jt_lo], nkv, kvh);
+    cp_async_commit();
+    for (int jt = jt_lo; jt <= jt_hi; jt++) {
+        const int cur = (jt - jt_lo) & 1;
+        if (jt < jt_hi) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key0 = jt * DK_PAGE;
+        if (key0 <= w_hi && key0 + DK_PAGE - 1 >= w_lo && warp * 16 < rows_here) {
+            const bf16* Ks = smem + cur * STAGE_ELEMS;
+            warp_attend<DK_PAGE>(qf, Ks, Ks + TILE_ELEMS, key0, lo, hi, sl2, m, l, acc);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    const float inv0 = ok0 ? 1.f / l[0] : 0.f, inv1 = ok1 ? 1.f / l[1] : 0.f;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++) {
+        const int d = nt * 8 + 2 * t;
+        if (ok0) *reinterpret_cast<uint32_t*>(out + (flat0 * nh + h) * HD + d) = pack_bf16(acc[nt][0] * inv0, acc[nt][1] * inv0);
+        if (ok1) *reinterpret_cast<uint32_t*>(out + (flat1 * nh + h) * HD + d) = pack_bf16(acc[nt][2] * inv1, acc[nt][3] * inv1);
+    }
+}
+
+// -------------------------------------------------------------------------------------- decode
+// grid (nsplit, nkv * mtiles, sequences), mtiles = ceil(G / 16). row_pos[b] is the position of
+// sequence b's one query token (its key is already cached); < 0 marks a padding row.
+// nsplit == 1: writes out directly. Otherwise writes float32 partials
+// ws_acc [(b*nh + head)*nsplit + split][HD] and ws_ml [...][2] = (max in log2 domain, row sum).
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
+                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2) {
+    extern __shared__ __align__(16) bf16 smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int G = nh / nkv, mtiles = (G + 15) / 16;
+    const int split = blockIdx.x, nsplit = gridDim.x;
+    const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
+    const int b = blockIdx.z;
+    const int head0 = kvh * G + mt * 16;
+    const int heads_here = min(16, G - mt * 16);
+    const int pos = row_pos[b];
+    const int* pt = page_table + (size_t)b * pt_stride;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    if (pos >= 0) {
+        const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
+        const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
+        const int jt0 = t_lo + split * per, jt1 = min(t_hi + 1, jt0 + per);  // [jt0, jt1)
+        if (jt0 < jt1) {
+            uint32_t qf[HD / 16][4];
+            const bf16* qb = q + ((size_t)b * nh + head0) * HD;
+            load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
+                         g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
+            const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
+            stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
+            cp_async_commit();
+            for (int jt = jt0; jt < jt1; jt++) {
+                const int cur = (jt - jt0) & 1;
+                if (jt + 1 < jt1) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
+                cp_async_commit();
+                cp_async_wait<1>();
+                __syncthreads();
+                const int key0 = jt * DK_PAGE + warp * 16;
+                if (key0 <= pos && key0 + 15 >= key_lo) {
+                    const bf16* Ks = smem + cur * STAGE_ELEMS + warp * 16 * KSTR;
+                    warp_attend<16>(qf, Ks, Ks + TILE_ELEMS, key0, lo, hi, sl2, m, l, acc);
+                }
+                __syncthreads();
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    // merge the four warps (each saw different keys) through shared memory
+    float* sm_m = reinterpret_cast<float*>(smem);  // [4][16]
+    float* sm_l = sm_m + 64;                       // [4][16]
+    float* sm_a = sm_l + 64;                       // [4][16][HD]
+    __syncthreads();
+    if (t == 0) {
+        sm_m[warp * 16 + g] = m[0];
+        sm_m[warp * 16 + g + 8] = m[1];
+        sm_l[warp * 16 + g] = l[0];
+        sm_l[warp * 16 + g + 8] = l[1];
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++) {
+        float* a0 = sm_a + ((size_t)(warp * 16 + g) * HD) + nt * 8 + 2 * t;
+        float* a1 = sm_a + ((size_t)(warp * 16 + g + 8) * HD) + nt * 8 + 2 * t;
+        a0[0] = acc[nt][0];
+        a0[1] = acc[nt][1];
+        a1[0] = acc[nt][2];
+        a1[1] = acc[nt][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < heads_here * HD; idx += blockDim.x) {
+        const int row = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + row]);
+        float L = 0.f, A = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float f = exp2f(sm_m[w * 16 + row] - M);
+                L += sm_l[w * 16 + row] * f;
+                A += sm_a[(size_t)(w * 16 + row) * HD + d] * f;
+            }
+        }
+        const size_t head = (size_t)b * nh + head0 + row;
+        if (nsplit == 1) {
+            out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        } else {
+            ws_acc[(head * nsplit + split) * HD + d] = A;
+            if (d == 0) {
+                ws_ml[(head * nsplit + split) * 2] = M;
+                ws_ml[(head * nsplit + split) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// grid (sequences * nh), HD threads or fewer looping: merges the splits of one head.
+__global__ void attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int nsplit) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t head = blockIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; s++) M = fmaxf(M, ws_ml[(head * nsplit + s) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float L = 0.f, A = 0.f;
+        if (M != -INFINITY) {
+            for (int s = 0; s < nsplit; s++) {
+                const float f = exp2f(ws_ml[(head * nsplit + s) * 2] - M);
+                L += ws_ml[(head * nsplit + s) * 2 + 1] * f;
+                A += ws_acc[(head * nsplit + s) * HD + d] * f;
+            }
+        }
+        out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+    }
+}
+
+static int ensure_smem_attr() {
+    static bool done = false;
+    if (done) return 0;
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    done = true;
+    return 0;
+}
+
+DK_EXPORT int dk_attn_head_dim() { return HD; }
+
+DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store, const void* v_store, const int* tiles,
+                                   int n_tiles, const int* cu_q, const int* seq_pos0, const int* page_table,
+                                   int pt_stride, int nh, int nkv, int window, float scale, cudaStream_t st) {
+    if (nh % nkv != 0) return (int)cudaErrorInvalidValue;
+    int e = ensure_smem_attr();
+    if (e) return e;
+    return dk_launch(attn_prefill_kernel, dim3(n_tiles, nh), dim3(128), SMEM_BYTES, st, (const bf16*)q, (bf16*)out,
+                     (const bf16*)k_store, (const bf16*)v_store, tiles, cu_q, seq_pos0, page_table, pt_stride, nh, nkv,
+                     window, scale * 1.4426950408889634f);
+}
+
+// ws_acc: n_seq*nh*nsplit*HD floats, ws_ml: n_seq*nh*nsplit*2 floats (unused when nsplit == 1)
+DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float* ws_ml, const void* k_store,
+                                  const void* v_store, const int* row_pos, const int* page_table, int pt_stride,
+                                  int n_seq, int nh, int nkv, int window, float scale, int nsplit, cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
+    int e = ensure_smem_attr();
+    if (e) return e;
+    const int G = nh / nkv, mtiles = (G + 15) / 16;
+    e = dk_launch(attn_decode_kernel, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), SMEM_BYTES, st, (const bf16*)q,
+                  (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
+                  nh, nkv, window, scale * 1.4426950408889634f);
+    if (e || nsplit == 1) return e;
+    return dk_launch(attn_combine_kernel, dim3(n_seq * nh), dim3(HD < 128 ? HD : 128), 0, st, (const float*)ws_acc,
+                     (const float*)ws_ml, (bf16*)out, nsplit);
+}

@@ -1,0 +1,215 @@
+// Memory-bound row kernels: embedding gather + RMSNorm, residual add + RMSNorm, SiLU(gate)*up,
+// and per-head RMSNorm + rotary position encoding + key/value cache write.
+//
+// The residual stream `h` is float32 for every model dtype; sums of squares, rsqrt, rotation and
+// the residual add are computed in float32. T is the activation/weight dtype (float or bf16).
+// Reference formulas (KrishP147/Dryft-Challenge-HTN-2026): engine/engine.py:107-115 (RMSNorm,
+// rotate-half RoPE), engine/fused.py:152-172 (add+norm), :175-188 (SiLU*up), :415-475 (q/k norm,
+// RoPE, cache write).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// h[row] = embed[tok[row]];  a[row] = rmsnorm(h[row]) * w
+template <typename T>
+__global__ void embed_rmsnorm_kernel(const int* tok, const T* __restrict__ embed,
+                                     const float* __restrict__ w, float eps, int H, int V,
+                                     float* h, T* a) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    int t = tok[row];
+    t = t < 0 ? 0 : (t >= V ? V - 1 : t);  // ids are validated on the host; never read out of bounds
+    const T* e = embed + (size_t)t * H;
+    float* hr = h + row * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_f(e[i]);
+        hr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    if (w == nullptr) return;
+    T* ar = a + row * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(hr[i] * rs * w[i]);
+}
+
+// h[row] += delta[row] (if delta);  a[out_row] = rmsnorm(h[row]) * w.
+// With `rows` the kernel gathers: out_row = blockIdx.x, row = rows[blockIdx.x], and h is not
+// written back (used for the final norm at the positions whose logits are wanted).
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* h, const T* delta,
+                                   const int* rows, const float* __restrict__ w, float eps,
+                                   int H, T* a) {
+    __shared__ float red[33];
+    extern __shared__ float vals[];  // H floats when gathering (h stays untouched)
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t out_row = blockIdx.x;
+    const size_t row = rows ? (size_t)rows[out_row] : out_row;
+    float* hr = h + row * H;
+    const T* dr = delta ? delta + row * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = hr[i];
+        if (dr) v += to_f(dr[i]);
+        if (rows) vals[i] = v; else hr[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    T* ar = a + out_row * H;
+    const float* src = rows ? vals : hr;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(src[i] * rs * w[i]);
+}
+
+// out[r, c] = silu(gu[r, c]) * gu[r, I + c],  gu rows are [gate | up] of width 2*I
+template <typename T>
+__global__ void silu_mul_kernel(const T* gu, T* out, size_t n, int I) {
+    pdl_wait();
+    pdl_launch_dependents();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    size_t r = idx / I, c = idx % I;
+    float g = to_f(gu[r * 2 * I + c]);
+    float u = to_f(gu[r * 2 * I + I + c]);
+    out[idx] = from_f<T>(g / (1.f + expf(-g)) * u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per (token, head) over nh query heads, nkv key heads and nkv value heads of a fused
+// projection row qkv[t] = [q | k | v]. Query and key heads: optional RMSNorm over the head
+// (weights qn / kn), optional rotate-half rotation by the angle table at the token's position.
+// q goes to q_out [T, nh*hd]; k and v go to the token's place in the paged cache (unless
+// write_kv == 0, for a layer that reads another layer's keys and values).
+// Tokens with position < 0 are padding: nothing is written for them.
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(const T* qkv, T* q_out,
+                                          const float* __restrict__ qn, const float* __restrict__ kn,
+                                          const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                          const int* row_pos, const int* row_seq,
+                                          const int* page_table, int pt_stride,
+                                          T* k_store, T* v_store, int n_tok, int nh,
+                                          int nkv, int hd, float eps, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long long)n_tok * heads) return;
+    const int t = (int)(wid / heads), hidx = (int)(wid % heads);
+    const int pos = row_pos[t];
+    if (pos < 0) return;
+    const int half = hd >> 1;
+    const T* x = qkv + (size_t)t * heads * hd + (size_t)hidx * hd;
+
+    T* dst;
+    if (hidx < nh) {
+        dst = q_out + ((size_t)t * nh + hidx) * hd;
+    } else {
+        if (!write_kv) return;
+        const int kvh = (hidx - nh) % nkv;
+        const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
+        T* store = hidx < nh + nkv ? k_store : v_store;
+        dst = store + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+    }
+    if (hidx >= nh + nkv) {  // value head: plain copy
+        for (int d = lane; d < hd; d += 32) dst[d] = x[d];
+        return;
+    }
+    // pairs (d, d + half), d = lane + 32*i; hd <= 256 gives at most 4 pairs a lane
+    float x1[4], x2[4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int d = lane + 32 * i;
+        x1[i] = d < half ? to_f(x[d]) : 0.f;
+        x2[i] = d < half ? to_f(x[d + half]) : 0.f;
+        ss += x1[i] * x1[i] + x2[i] * x2[i];
+    }
+    const float* nw = hidx < nh ? qn : kn;
+    if (nw) {
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int d = lane + 32 * i;
+            if (d < half) {
+                x1[i] = x1[i] * rs * nw[d];
+                x2[i] = x2[i] * rs * nw[d + half];
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int d = lane + 32 * i;
+        if (d < half) {
+            float o1 = x1[i], o2 = x2[i];
+            if (cos_t) {
+                const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
+                o1 = x1[i] * c - x2[i] * s;
+                o2 = x2[i] * c + x1[i] * s;
+            }
+            dst[d] = from_f<T>(o1);
+            dst[d + half] = from_f<T>(o2);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[i] = src[rows[i]] for rows of H floats (positions whose logits are wanted)
+__global__ void gather_rows_f32_kernel(const float* src, const int* rows,
+                                       float* out, int H) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* s = src + (size_t)rows[blockIdx.x] * H;
+    float* o = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = s[i];
+}
+
+// ---------------------------------------------------------------------------------------------
+#define DISPATCH_T(dtype, ...)                         \
+    if ((dtype) == 0) { typedef float T; __VA_ARGS__; } \
+    else { typedef bf16 T; __VA_ARGS__; }
+
+static inline int row_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+DK_EXPORT int dk_embed_rmsnorm(int dtype, const int* tok, const void* embed, const float* w, float eps,
+                               int n_tok, int H, int V, float* h, void* a, cudaStream_t st) {
+    DISPATCH_T(dtype, return dk_launch(embed_rmsnorm_kernel<T>, dim3(n_tok), dim3(row_threads(H)), 0, st, tok,
+                                       (const T*)embed, w, eps, H, V, h, (T*)a));
+}
+
+DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const int* rows, const float* w, float eps,
+                             int n_rows, int H, void* a, cudaStream_t st) {
+    size_t smem = rows ? (size_t)H * sizeof(float) : 0;
+    if (smem > 48 * 1024) {
+        DISPATCH_T(dtype, cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem));
+    }
+    DISPATCH_T(dtype, return dk_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(row_threads(H)), smem, st, h,
+                                       (const T*)delta, rows, w, eps, H, (T*)a));
+}
+
+DK_EXPORT int dk_silu_mul(int dtype, const void* gu, void* out, long long n_rows, int I, cudaStream_t st) {
+    size_t n = (size_t)n_rows * I;
+    DISPATCH_T(dtype, return dk_launch(silu_mul_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
+                                       (const T*)gu, (T*)out, n, I));
+}
+
+DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, const float* qn, const float* kn,
+                                    const float* cos_t, const float* sin_t, const int* row_pos, const int* row_seq,
+                                    const int* page_table, int pt_stride, void* k_store, void* v_store, int n_tok,
+                                    int nh, int nkv, int hd, float eps, int write_kv, cudaStream_t st) {
+    if (hd % 2 != 0 || hd > 256) return (int)cudaErrorInvalidValue;
+    long long warps = (long long)n_tok * (nh + 2 * nkv);
+    unsigned blocks = (unsigned)((warps + 3) / 4);
+    DISPATCH_T(dtype, return dk_launch(qk_norm_rope_write_kernel<T>, dim3(blocks), dim3(128), 0, st, (const T*)qkv,
+                                       (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
+                                       (T*)k_store, (T*)v_store, n_tok, nh, nkv, hd, eps, write_kv));
+}
+
+DK_EXPORT int dk_gather_rows_f32(const float* src, const int* rows, float* out, int n_rows, int H, cudaStream_t st) {
+    return dk_launch(gather_rows_f32_kernel, dim3(n_rows), dim3(256), 0, st, src, rows, out, H);
+}

@@ -1,0 +1,96 @@
+"""A causal language model put together from a ``ModelSpec``: embedding, blocks run in schedule
+order, final norm, output head. ``forward`` runs one step over the token rows a ``StepContext``
+describes and returns float32 logits at the wanted rows (reference: engine/engine.py:459-503).
+"""
+import torch
+
+from ..csrc import api
+from ..parts import ParamDecl, Runtime, build_part
+from ..parts.linear import STORE_F32, linear
+
+
+class CausalLM:
+    def __init__(self, spec, dtype=torch.bfloat16, device="cuda"):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype must be torch.float32 or torch.bfloat16, not {dtype}")
+        self.spec = spec
+        self.rt = Runtime(torch.device(device), dtype)
+        self.blocks = [build_part(ls, self.rt) for ls in spec.layers]
+        self.final_norm = build_part(spec.final_norm, self.rt)
+        n_entries = max(e.cache for e in spec.schedule) + 1
+        owners = {}
+        for e in spec.schedule:
+            if not 0 <= e.layer < len(self.blocks):
+                raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.blocks)}")
+            if e.writes:
+                if e.cache in owners:
+                    raise ValueError(f"cache entry {e.cache} is written by two schedule entries")
+                owners[e.cache] = e.layer
+        for e in spec.schedule:
+            if e.cache not in owners:
+                raise ValueError(f"cache entry {e.cache} is read but never written")
+            if self.blocks[e.layer].cache_requests() != self.blocks[owners[e.cache]].cache_requests():
+                raise ValueError(f"layer {e.layer} cannot use cache entry {e.cache}: its owner stores something else")
+        self._entry_requests = [self.blocks[owners[c]].cache_requests() for c in range(n_entries)]
+        self.embed = self.head = None
+        self.tied = None
+
+    # -- parameters --------------------------------------------------------------------------
+    def param_decls(self, tied):
+        """Checkpoint name -> ParamDecl for the whole model."""
+        s = self.spec
+        out = {s.embed_name: ParamDecl(s.embed_name, (s.vocab_size, s.hidden_size), "matrix")}
+        for ls, blk in zip(s.layers, self.blocks):
+            for p in blk.param_decls():
+                out[ls.prefix + p.name] = p
+        for p in self.final_norm.param_decls():
+            out[s.final_norm_prefix + p.name] = p
+        if not tied:
+            out[s.head_name] = ParamDecl(s.head_name, (s.vocab_size, s.hidden_size), "matrix")
+        return out
+
+    def bind(self, tensors, tied):
+        s = self.spec
+        self.tied = tied
+        self.embed = tensors.pop(s.embed_name).contiguous()
+        self.head = self.embed if tied else tensors.pop(s.head_name).contiguous()
+        for ls, blk in zip(s.layers, self.blocks):
+            n = len(ls.prefix)
+            blk.bind({k[n:]: tensors.pop(k) for k in [k for k in tensors if k.startswith(ls.prefix)]})
+        n = len(s.final_norm_prefix)
+        self.final_norm.bind({k[n:]: tensors.pop(k) for k in [k for k in tensors if k.startswith(s.final_norm_prefix)]})
+
+    def entry_requests(self):
+        return self._entry_requests
+
+    def prepare(self, max_positions):
+        for b in self.blocks:
+            b.prepare(max_positions)
+
+    def weight_bytes_per_step(self):
+        """Bytes of weights a decode step reads: every matrix once, the embedding only when it is
+        also the head."""
+        total = self.head.numel() * self.head.element_size()
+        for b in self.blocks:
+            for t in (b.mixer.__dict__, b.feed_forward.__dict__):
+                total += sum(v.numel() * v.element_size() for v in t.values() if isinstance(v, torch.Tensor))
+        return total
+
+    # -- one step ----------------------------------------------------------------------------
+    def forward(self, ctx, cache):
+        s, rt = self.spec, self.rt
+        h = torch.empty((ctx.n_tok, s.hidden_size), dtype=torch.float32, device=rt.device)
+        a = torch.empty((ctx.n_tok, s.hidden_size), dtype=rt.dtype, device=rt.device)
+        first = self.blocks[s.schedule[0].layer]
+        fused = getattr(first.norm_in, "weight", None) is not None and hasattr(first.norm_in.spec, "eps")
+        api.embed_rmsnorm(ctx.tok, self.embed, first.norm_in.weight if fused else None,
+                          first.norm_in.spec.eps if fused else 0.0, h, a)
+        pending = None
+        for i, e in enumerate(s.schedule):
+            pending = self.blocks[e.layer].forward(ctx, h, pending, cache.views(e.cache), e.writes,
+                                                   a if (i == 0 and fused) else None)
+        if ctx.n_want == 0:
+            return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
+        an = torch.empty((ctx.n_want, s.hidden_size), dtype=rt.dtype, device=rt.device)
+        self.final_norm.add_forward(h, pending, an, rows=ctx.want_rows)
+        return linear(an, self.head, STORE_F32)

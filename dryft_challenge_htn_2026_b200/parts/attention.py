@@ -1,0 +1,94 @@
+"""Causal grouped-query attention mixer over the paged key/value cache.
+
+forward = fused q/k/v projection -> per-head q/k norm + rotary + cache write (one kernel) ->
+attention over the cache -> output projection (reference: engine/engine.py:472-493; the residual
+add belongs to the block). The same forward serves whole prompts, continued chunks and single
+tokens: the step context says where each token row sits, the cache says what came before.
+"""
+import torch
+
+from ..cache.requests import KVRequest
+from ..config.specs import AttentionSpec
+from ..csrc import api
+from .base import ParamDecl, Part, build_part, register_part
+from .linear import linear
+
+
+class GQAAttention(Part):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} key/value heads")
+        if rt.dtype == torch.bfloat16 and (s.head_dim % 16 or s.head_dim > 256):
+            raise ValueError(f"bfloat16 attention kernels take head sizes in steps of 16 up to 256, not {s.head_dim}")
+        if s.head_dim % 2 or s.head_dim > 256:
+            raise ValueError(f"attention kernels take even head sizes up to 256, not {s.head_dim}")
+        if rt.dtype == torch.bfloat16 and s.hidden_size % 8:
+            raise ValueError(f"bfloat16 projections need a hidden size that is a multiple of 8, not {s.hidden_size}")
+        self.q_norm = build_part(s.qk_norm, rt) if s.qk_norm is not None else None
+        self.k_norm = build_part(s.qk_norm, rt) if s.qk_norm is not None else None
+        self.position = build_part(s.position, rt) if s.position is not None else None
+        self.max_positions = 0
+
+    def param_decls(self):
+        s = self.spec
+        d = [ParamDecl("q_proj.weight", (s.num_heads * s.head_dim, s.hidden_size)),
+             ParamDecl("k_proj.weight", (s.num_kv_heads * s.head_dim, s.hidden_size)),
+             ParamDecl("v_proj.weight", (s.num_kv_heads * s.head_dim, s.hidden_size)),
+             ParamDecl("o_proj.weight", (s.hidden_size, s.num_heads * s.head_dim))]
+        if self.q_norm is not None:
+            d += [ParamDecl("q_norm." + p.name, p.shape, p.init, p.keep_float32) for p in self.q_norm.param_decls()]
+            d += [ParamDecl("k_norm." + p.name, p.shape, p.init, p.keep_float32) for p in self.k_norm.param_decls()]
+        return d
+
+    def bind(self, tensors):
+        # one fused projection [q; k; v] as the reference does (engine/engine.py:300-302)
+        self.w_qkv = torch.cat([tensors.pop("q_proj.weight"), tensors.pop("k_proj.weight"),
+                                tensors.pop("v_proj.weight")], 0).contiguous()
+        self.w_o = tensors.pop("o_proj.weight").contiguous()
+        if self.q_norm is not None:
+            self.q_norm.bind({"weight": tensors.pop("q_norm.weight")})
+            self.k_norm.bind({"weight": tensors.pop("k_norm.weight")})
+
+    def cache_requests(self):
+        s = self.spec
+        return [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype)]
+
+    def prepare(self, max_positions):
+        self.max_positions = max_positions
+        if self.position is not None and getattr(self.position, "fused_tables", False):
+            self.position.tables(max_positions)
+
+    def forward(self, ctx, views, a, writes=True):
+        s, kv = self.spec, views[0]
+        nh, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        table = ctx.tables[kv.group]
+        qkv = linear(a, self.w_qkv)
+        cos = sin = None
+        if self.position is not None:
+            if getattr(self.position, "fused_tables", False):
+                cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
+            else:
+                self.position.apply(qkv, ctx, nh, nkv, hd)
+        q = torch.empty((ctx.n_tok, nh * hd), dtype=a.dtype, device=a.device)
+        api.qk_norm_rope_write(qkv, q, self.q_norm.weight if self.q_norm else None,
+                               self.k_norm.weight if self.k_norm else None, cos, sin, ctx.row_pos, ctx.row_seq, table,
+                               kv.k, kv.v, nh, nkv, hd, s.qk_norm.eps if s.qk_norm else 0.0, write_kv=writes)
+        o = torch.empty_like(q)
+        window = s.window or 0
+        if a.dtype == torch.float32:
+            api.attention_generic(q, o, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, nh, nkv, hd, window, s.scale)
+        elif ctx.is_decode:
+            nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
+            ws_acc, ws_ml = ctx.scratch(("attn_decode", nh, hd, nsplit),
+                                        lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, a.device))
+            api.attention_decode_bf16(q, o, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window, s.scale, nsplit,
+                                      ws_acc, ws_ml)
+        else:
+            api.attention_prefill_bf16(q, o, kv.k, kv.v, ctx.tiles, ctx.cu_q, ctx.seq_pos0, table, nh, nkv, hd,
+                                       window, s.scale)
+        return linear(o, self.w_o)
+
+
+register_part(AttentionSpec, GQAAttention)
