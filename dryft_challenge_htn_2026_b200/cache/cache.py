@@ -156,6 +156,8 @@ class Cache:
             g.trim(slot, self.length[slot])
 
     def end(self, slot):
+        if slot not in self.length:
+            raise ValueError(f"slot {slot} ended but not live")
         for g in self.groups:
             g.end(slot)
         del self.length[slot]

@@ -71,7 +71,8 @@ def run_batch(backend, prompts, params, seeds):
                 break
             w, pending = queue.popleft()
             row, newly = tracker.accept(w, pending.wait())
-            yield row
+            if any(t is not None for t in row):   # a step launched for sequences that had all ended
+                yield row
             repack = repack or bool(newly)
             if repack and not queue:
                 who = tracker.active(who)

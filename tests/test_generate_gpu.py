@@ -1,0 +1,125 @@
+"""Generation through the Python entry point: greedy and sampled tokens against the plain
+implementation, stop tokens, batches one after another, long decoding across page boundaries,
+graph replay against plain launches."""
+import pytest
+import torch
+
+import dryft_challenge_htn_2026_b200 as dk
+import plain_qwen3 as plain
+from dryft_challenge_htn_2026_b200.sampling import request_seed
+from helpers import TINY, make_folder, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def teacher_forced_gap(cfg, t, prompt, emitted):
+    """max over steps of (best plain logit - plain logit of the emitted token): 0 when the engine
+    picked what the plain implementation would."""
+    logits = plain.forward(cfg, t, list(prompt) + list(emitted[:-1]))[len(prompt) - 1:]
+    picked = logits.gather(1, torch.tensor(emitted).view(-1, 1)).squeeze(1)
+    return float((logits.max(-1).values - picked).max())
+
+
+@pytest.mark.parametrize("name,lens,n", [("A", [5, 9, 13], 8), ("B", [1, 7, 16, 31], 12), ("C", [3, 70, 33], 40)])
+def test_greedy_float32_equals_plain(tmp_path, name, lens, n):
+    folder = make_folder(tmp_path, name, seed=7)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY[name]["vocab_size"], L, 10 + i) for i, L in enumerate(lens)]
+    eng = dk.Engine(folder, dtype=torch.float32)
+    steps = list(eng.generate(prompts, n))
+    assert len(steps) == n and all(len(s) == len(prompts) for s in steps)
+    for i, p in enumerate(prompts):
+        emitted = [s[i] for s in steps]
+        want = plain.greedy(cfg, t, p, n)
+        if emitted != want:          # a near-tie may flip in float32: then the gap must be rounding-small
+            assert teacher_forced_gap(cfg, t, p, emitted) < 1e-4, (i, emitted, want)
+    again = list(eng.generate(prompts, n))
+    assert again == steps                                             # no state leaks between calls
+    assert list(eng.generate(prompts, 0)) == []
+    # one request alone gives what it gave in the batch
+    alone = [s[0] for s in eng.generate([prompts[1]], n)]
+    assert alone == [s[1] for s in steps]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_bfloat16_stays_within_rounding_of_plain(tmp_path, name):
+    folder = make_folder(tmp_path, name, seed=8)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY[name]["vocab_size"], L, 20 + i) for i, L in enumerate([4, 40, 66, 17, 9])]
+    eng = dk.Engine(folder, dtype=torch.bfloat16)
+    steps = list(eng.generate(prompts, 24))
+    scale = max(1.0, float(plain.forward(cfg, t, prompts[1]).abs().max()))
+    for i, p in enumerate(prompts):
+        assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale
+
+
+def test_graph_replay_equals_plain_launches(tmp_path):
+    folder = make_folder(tmp_path, "B", seed=9)
+    prompts = [random_tokens(384, L, 30 + i) for i, L in enumerate([3, 50, 64])]
+    for dtype in (torch.float32, torch.bfloat16):
+        a = list(dk.Engine(folder, dtype=dtype, use_graph=True).generate(prompts, 20, temperature=0.9, seed=3))
+        b = list(dk.Engine(folder, dtype=dtype, use_graph=False).generate(prompts, 20, temperature=0.9, seed=3))
+        assert a == b
+
+
+def test_temperature_sampling_follows_the_plain_gumbel_rule(tmp_path):
+    folder = make_folder(tmp_path, "B", seed=10)
+    cfg, t = plain.read_model(folder)
+    lens, n, temp, seed = [1, 7, 16, 31], 12, 0.8, 1234
+    prompts = [random_tokens(384, L, 40 + i) for i, L in enumerate(lens)]
+    eng = dk.Engine(folder, dtype=torch.float32)
+    steps = list(eng.generate(prompts, n, temperature=temp, seed=seed))
+    assert steps != list(eng.generate(prompts, n, temperature=temp, seed=seed + 1))
+    assert steps == list(eng.generate(prompts, n, temperature=temp, seed=seed))
+    for i, p in enumerate(prompts):
+        emitted = [s[i] for s in steps]
+        logits = plain.forward(cfg, t, p + emitted[:-1])[len(p) - 1:]
+        for k, tok in enumerate(emitted):
+            want, z = plain.gumbel_argmax(logits[k], temp, request_seed(seed, i), len(p) + k)
+            assert tok == want or abs(z[tok] - z[want]) < 1e-3, (i, k, tok, want)
+    # a request draws the same tokens alone as in the batch (its seed goes with its index)
+    alone = [s[0] for s in eng.generate([prompts[2]], n, temperature=temp, seed=seed, first_index=2)]
+    assert alone == [s[2] for s in steps]
+
+
+def test_stop_tokens_and_batches_one_after_another(tmp_path):
+    folder = make_folder(tmp_path, "A", seed=11)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(256, 3 + (5 * i) % 23, 50 + i) for i in range(11)]
+    eng = dk.Engine(folder, dtype=torch.float32)
+    free = dk.Engine(folder, dtype=torch.float32).generate_all(prompts, 30, batch_size=16)
+    # pick as stop tokens ids that some sequences emit in the middle
+    stops = {free[0][5], free[3][11], free[7][2]}
+    outs = eng.generate_all(prompts, 30, stop_token_ids=stops, batch_size=4)    # 3 batches on reused slots
+    assert len(outs) == 11
+    for i, o in enumerate(outs):
+        cut = next((k for k, tok in enumerate(free[i]) if tok in stops), 29)
+        assert o == free[i][:cut + 1], i                               # the stop token is the last one returned
+    assert eng.runner.cache.slots.n_live == 0
+    assert eng.runner.cache.pages_free() == [eng.runner.cache.num_pages]
+
+
+def test_long_decoding_across_pages(tmp_path):
+    folder = make_folder(tmp_path, "C", seed=12)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(300, 5, 60), random_tokens(300, 62, 61)]
+    for dtype, bound in ((torch.float32, 1e-4), (torch.bfloat16, None)):
+        eng = dk.Engine(folder, dtype=dtype)
+        steps = list(eng.generate(prompts, 200))                      # lengths pass 64, 128, 192, 256 and the window
+        scale = max(1.0, float(plain.forward(cfg, t, prompts[1]).abs().max()))
+        for i, p in enumerate(prompts):
+            gap = teacher_forced_gap(cfg, t, p, [s[i] for s in steps])
+            assert gap <= (bound if bound is not None else 0.12 * scale), (dtype, i, gap)
+
+
+def test_engine_refuses_bad_input(tmp_path):
+    folder = make_folder(tmp_path, "A", seed=13)
+    eng = dk.Engine(folder, dtype=torch.float32)
+    with pytest.raises(ValueError):
+        list(eng.generate([[1, 2], []], 3))
+    with pytest.raises(ValueError):
+        list(eng.generate([[1, 999]], 3))                             # id outside the vocabulary
+    small = dk.Engine(folder, dtype=torch.float32, max_tokens=64)
+    with pytest.raises(ValueError):
+        list(small.generate([[1] * 60], 30))
+    assert len(list(small.generate([[1] * 10], 5))) == 5

@@ -1,0 +1,330 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same operation, at
+sizes other than the models' (odd row counts, widths that are no power of two, shuffled pages)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from dryft_challenge_htn_2026_b200.csrc import api
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+PAGE = api.PAGE
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+def close(got, ref, dtype, what=""):
+    tol = (1e-5 if dtype == torch.float32 else 2e-2) * max(1.0, float(ref.abs().max()))
+    err = float((got.float() - ref.float()).abs().max())
+    assert err <= tol, f"{what}: max error {err} > {tol}"
+
+
+def rms(x, w, eps):
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,V", [(1, 40, 50), (37, 2560, 300), (130, 72, 1000)])
+def test_embed_rmsnorm(dtype, T, H, V):
+    embed, w = rnd(V, H, dtype=dtype, seed=1), 1 + 0.1 * rnd(H, seed=2)
+    tok = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    h = torch.empty(T, H, device=DEV)
+    a = torch.empty(T, H, dtype=dtype, device=DEV)
+    api.embed_rmsnorm(tok, embed, w, 1e-5, h, a)
+    assert torch.equal(h, embed[tok.long()].float())
+    close(a, rms(h, w, 1e-5), dtype, "embed_rmsnorm")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H", [(1, 64), (33, 2560), (70, 200)])
+def test_add_rmsnorm_and_row_gather(dtype, T, H):
+    h0, delta, w = rnd(T, H, seed=3, scale=3.0), rnd(T, H, dtype=dtype, seed=4), 1 + 0.1 * rnd(H, seed=5)
+    h = h0.clone()
+    a = torch.empty(T, H, dtype=dtype, device=DEV)
+    api.add_rmsnorm(h, delta, w, 1e-6, a)
+    ref_h = h0 + delta.float()
+    assert torch.allclose(h, ref_h, atol=1e-6)
+    close(a, rms(ref_h, w, 1e-6), dtype, "add_rmsnorm")
+    api.add_rmsnorm(h, None, w, 1e-6, a)                                  # norm only
+    assert torch.allclose(h, ref_h, atol=1e-6)
+    close(a, rms(ref_h, w, 1e-6), dtype, "rmsnorm")
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32, device=DEV)
+    h = h0.clone()
+    ag = torch.empty(3, H, dtype=dtype, device=DEV)
+    api.add_rmsnorm(h, delta, w, 1e-6, ag, rows)
+    assert torch.equal(h, h0)                                             # gathering leaves h alone
+    close(ag, rms(ref_h[rows.long()], w, 1e-6), dtype, "gathered add_rmsnorm")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(dtype):
+    gu = rnd(45, 2 * 200, dtype=dtype, seed=6, scale=3.0)
+    out = torch.empty(45, 200, dtype=dtype, device=DEV)
+    api.silu_mul(gu, out)
+    g, u = gu[:, :200].float(), gu[:, 200:].float()
+    close(out, g / (1 + torch.exp(-g)) * u, dtype, "silu_mul")
+
+
+# --------------------------------------------------------------------------- paged cache helpers
+def paged_setup(lens_before, lens_new, nkv, hd, dtype, seed=0, extra_pages=3):
+    """Random sequences with ``lens_before`` cached tokens and ``lens_new`` new ones, pages handed
+    out in shuffled order. Returns dense k/v per sequence and the step's index arrays."""
+    rs = np.random.RandomState(seed)
+    n_seq = len(lens_new)
+    total = [b + n for b, n in zip(lens_before, lens_new)]
+    need = [(t + PAGE - 1) // PAGE for t in total]
+    n_pages = sum(need) + extra_pages
+    perm = rs.permutation(n_pages).tolist()
+    width = max(need)
+    table = -np.ones((n_seq, width), dtype=np.int32)
+    for i, n in enumerate(need):
+        table[i, :n] = [perm.pop() for _ in range(n)]
+    row_seq = np.repeat(np.arange(n_seq), lens_new).astype(np.int32)
+    row_pos = np.concatenate([np.arange(b, b + n) for b, n in zip(lens_before, lens_new)]).astype(np.int32)
+    cu = np.concatenate([[0], np.cumsum(lens_new)]).astype(np.int32)
+    k_store = torch.zeros(n_pages, nkv, PAGE, hd, dtype=dtype, device=DEV)
+    v_store = torch.zeros_like(k_store)
+    dense_k = [rnd(t, nkv, hd, dtype=dtype, seed=seed * 100 + 2 * i) for i, t in enumerate(total)]
+    dense_v = [rnd(t, nkv, hd, dtype=dtype, seed=seed * 100 + 2 * i + 1) for i, t in enumerate(total)]
+    for i in range(n_seq):
+        for p in range(total[i]):
+            k_store[table[i, p // PAGE], :, p % PAGE] = dense_k[i][p]
+            v_store[table[i, p // PAGE], :, p % PAGE] = dense_v[i][p]
+    tiles = sorted(((lens_before[i] + min(q0 + 64, lens_new[i]), i, q0) for i in range(n_seq)
+                    for q0 in range(0, lens_new[i], 64)), reverse=True)
+    t = lambda a: torch.tensor(np.asarray(a), dtype=torch.int32, device=DEV)
+    return dict(table=t(table), row_seq=t(row_seq), row_pos=t(row_pos), cu_q=t(cu), pos0=t(lens_before),
+                tiles=t([(x[1], x[2]) for x in tiles]).reshape(-1, 2), k_store=k_store, v_store=v_store,
+                dense_k=dense_k, dense_v=dense_v, n_tok=int(cu[-1]))
+
+
+def ref_attention(q, s, nh, nkv, hd, window, scale):
+    """q [T, nh*hd] -> [T, nh*hd] in float32 from the dense per-sequence keys and values."""
+    out = torch.zeros(q.shape[0], nh, hd, device=DEV)
+    G = nh // nkv
+    qf = q.float().view(-1, nh, hd)
+    for t in range(q.shape[0]):
+        i, p = int(s["row_seq"][t]), int(s["row_pos"][t])
+        lo = max(0, p - window + 1) if window else 0
+        K, V = s["dense_k"][i][lo:p + 1].float(), s["dense_v"][i][lo:p + 1].float()
+        for h in range(nh):
+            w = torch.softmax((K[:, h // G] @ qf[t, h]) * scale, 0)
+            out[t, h] = w @ V[:, h // G]
+    return out.view(q.shape[0], nh * hd)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (6, 1, 48), (3, 3, 128)])
+def test_qk_norm_rope_write(dtype, nh, nkv, hd):
+    before, new = [0, 70, 5], [9, 3, 130]
+    s = paged_setup(before, new, nkv, hd, dtype, seed=7)
+    s["k_store"].zero_(), s["v_store"].zero_()
+    T = s["n_tok"]
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=8)
+    qn, kn = 1 + 0.1 * rnd(hd, seed=9), 1 + 0.1 * rnd(hd, seed=10)
+    cos, sin = plain.rope_tables(1e4, hd, 256)
+    cos_h, sin_h = cos[:, :hd // 2].contiguous().to(DEV), sin[:, :hd // 2].contiguous().to(DEV)
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    # a padding row in the middle must leave no trace
+    s["row_pos"][4] = -1
+    api.qk_norm_rope_write(qkv, q_out, qn, kn, cos_h, sin_h, s["row_pos"], s["row_seq"], s["table"], s["k_store"],
+                           s["v_store"], nh, nkv, hd, 1e-6)
+    x = qkv.float().view(T, nh + 2 * nkv, hd)
+    pos = s["row_pos"].long().clamp(min=0).cpu()
+    c, sn = cos[pos].to(DEV), sin[pos].to(DEV)
+    q_ref = plain.apply_rope(rms(x[:, :nh], qn, 1e-6), c, sn)
+    k_ref = plain.apply_rope(rms(x[:, nh:nh + nkv], kn, 1e-6), c, sn)
+    v_ref = x[:, nh + nkv:]
+    keep = s["row_pos"] >= 0
+    close(q_out.view(T, nh, hd)[keep], q_ref[keep], dtype, "q")
+    for t in range(T):
+        i, p = int(s["row_seq"][t]), int(s["row_pos"][t])
+        if p < 0:
+            continue
+        page = int(s["table"][i, p // PAGE])
+        close(s["k_store"][page, :, p % PAGE], k_ref[t], dtype, f"k row {t}")
+        close(s["v_store"][page, :, p % PAGE], v_ref[t], dtype, f"v row {t}")
+    # nothing else was written: the padding row's place and the unused pages are still zero
+    written = sum(1 for t in range(T) if int(s["row_pos"][t]) >= 0)
+    assert int((s["k_store"].float().abs().sum((1, 3)) > 0).sum()) == written
+    # without norm, rotation or writing
+    k_before = s["k_store"].clone()
+    api.qk_norm_rope_write(qkv, q_out, None, None, None, None, s["row_pos"], s["row_seq"], s["table"], s["k_store"],
+                           s["v_store"], nh, nkv, hd, 1e-6, write_kv=False)
+    assert torch.equal(q_out.view(T, nh, hd)[keep], qkv.view(T, nh + 2 * nkv, hd)[:, :nh][keep])
+    assert torch.equal(s["k_store"], k_before)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 0), (8, 2, 32, 50), (2, 2, 256, 0)])
+def test_attention_generic(dtype, nh, nkv, hd, window):
+    s = paged_setup([0, 100, 7, 64], [70, 3, 1, 1], nkv, hd, dtype, seed=11)
+    q = rnd(s["n_tok"], nh * hd, dtype=dtype, seed=12)
+    out = torch.empty_like(q)
+    api.attention_generic(q, out, s["k_store"], s["v_store"], s["row_pos"], s["row_seq"], s["table"], nh, nkv, hd,
+                          window, hd ** -0.5)
+    close(out, ref_attention(q, s, nh, nkv, hd, window, hd ** -0.5), dtype, "attention_generic")
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, 0), (8, 2, 128, 0), (6, 2, 48, 0), (3, 1, 64, 90), (4, 4, 32, 10),
+                                              (20, 1, 16, 0)])
+def test_attention_prefill_bf16(nh, nkv, hd, window):
+    s = paged_setup([0, 100, 0, 64, 130], [70, 150, 1, 64, 5], nkv, hd, torch.bfloat16, seed=13)
+    q = rnd(s["n_tok"], nh * hd, dtype=torch.bfloat16, seed=14)
+    out = torch.full_like(q, float("nan"))
+    api.attention_prefill_bf16(q, out, s["k_store"], s["v_store"], s["tiles"], s["cu_q"], s["pos0"], s["table"], nh,
+                               nkv, hd, window, hd ** -0.5)
+    close(out, ref_attention(q, s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_prefill_bf16")
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window,nsplit", [(4, 2, 16, 0, 1), (32, 8, 128, 0, 4), (6, 2, 48, 0, 8),
+                                                     (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 32)])
+def test_attention_decode_bf16(nh, nkv, hd, window, nsplit):
+    before = [0, 63, 64, 300, 1000, 5]
+    s = paged_setup(before, [1] * len(before), nkv, hd, torch.bfloat16, seed=15)
+    n = len(before)
+    q = rnd(n + 2, nh * hd, dtype=torch.bfloat16, seed=16)           # two padding rows at the end
+    row_pos = torch.cat([s["row_pos"], torch.tensor([-1, -1], dtype=torch.int32, device=DEV)])
+    table = torch.cat([s["table"], -torch.ones(2, s["table"].shape[1], dtype=torch.int32, device=DEV)])
+    out = torch.full_like(q, float("nan"))
+    ws_acc, ws_ml = api.attention_decode_ws(n + 2, nh, hd, nsplit, DEV)
+    api.attention_decode_bf16(q, out, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd, window, hd ** -0.5,
+                              nsplit, ws_acc, ws_ml)
+    close(out[:n], ref_attention(q[:n], s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_decode_bf16")
+    assert float(out[n:].float().abs().max()) == 0.0                 # padding rows give zeros, not garbage
+
+
+@pytest.mark.parametrize("kernel", ["generic_f32", "prefill", "decode"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
+    """One key among hundreds matches the query strongly, so the output must be that key's value:
+    a kernel that drops a page, a split or the last key of a window shows it at once."""
+    nh = nkv = 1
+    hd = 32
+    L = 777
+    dtype = torch.float32 if kernel == "generic_f32" else torch.bfloat16
+    for target, window, visible in [(3, 0, True), (700, 0, True), (L - 1, 0, True), (L - 50, 50, True),
+                                    (L - 51, 50, False), (64 * 5, 0, True), (64 * 5 - 1, 0, True)]:
+        s = paged_setup([L - 1], [1], nkv, hd, dtype, seed=17)
+        page, slot = int(s["table"][0, target // PAGE]), target % PAGE
+        direction = torch.zeros(hd, device=DEV)
+        direction[5] = 1.0
+        s["k_store"][:, :, :, :] *= 0.05
+        s["k_store"][page, 0, slot] = (direction * 40).to(dtype)
+        marker = torch.full((hd,), 7.0, device=DEV)
+        s["v_store"][page, 0, slot] = marker.to(dtype)
+        q = (direction * 10).to(dtype).view(1, hd)
+        out = torch.empty_like(q)
+        if kernel == "generic_f32":
+            api.attention_generic(q, out, s["k_store"], s["v_store"], s["row_pos"], s["row_seq"], s["table"], 1, 1, hd,
+                                  window, hd ** -0.5)
+        elif kernel == "prefill":
+            api.attention_prefill_bf16(q, out, s["k_store"], s["v_store"], s["tiles"], s["cu_q"], s["pos0"], s["table"],
+                                       1, 1, hd, window, hd ** -0.5)
+        else:
+            ws = api.attention_decode_ws(1, 1, hd, 8, DEV)
+            api.attention_decode_bf16(q, out, s["k_store"], s["v_store"], s["row_pos"], s["table"], 1, 1, hd, window,
+                                      hd ** -0.5, 8, *ws)
+        hit = float((out.float() - marker).abs().max()) < 0.1
+        assert hit == visible, f"{kernel}: key {target} window {window}: expected visible={visible}"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 300, 72), (64, 100, 200), (130, 96, 257)])
+def test_sgemm(M, N, K):
+    x, w = rnd(M, K, seed=18), rnd(N, K, seed=19)
+    out = torch.empty(M, N, device=DEV)
+    api.sgemm(x, w, out)
+    ref = (x.double() @ w.double().T).float()
+    close(out, ref, torch.float32, "sgemm")
+    w2 = rnd(2 * N, K, seed=20, scale=0.3)
+    api.sgemm(x, w2, out, api.MODE_SILU)
+    y = x.double() @ w2.double().T
+    g, u = y[:, :N], y[:, N:]
+    close(out, (g / (1 + torch.exp(-g)) * u).float(), torch.float32, "sgemm silu")
+    # a row's result does not depend on the rows beside it
+    one = torch.empty(1, N, device=DEV)
+    api.sgemm(x[M // 2:M // 2 + 1].contiguous(), w, one)
+    api.sgemm(x, w, out)
+    assert torch.equal(one[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,K", [(64, 64), (300, 72), (200, 2560), (2560, 9728 // 4 + 8)])
+def test_gemv_bf16(M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=21), rnd(N, K, dtype=torch.bfloat16, seed=22, scale=0.05)
+    ref = x.float() @ w.float().T
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    api.gemv_bf16(x, w, out)
+    close(out, ref, torch.bfloat16, "gemv store")
+    out32 = torch.empty(M, N, device=DEV)
+    api.gemv_bf16(x, w, out32, api.MODE_STORE_F32)
+    assert float((out32 - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))   # float32 accumulate and store
+    for plan in [(1, 1), (2, 2), (1, 8), (8, 1)]:
+        api.gemv_bf16(x, w, out32, api.MODE_STORE_F32, plan=plan)
+        assert float((out32 - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
+    if N % 2 == 0:
+        half = N // 2
+        o = torch.empty(M, half, dtype=torch.bfloat16, device=DEV)
+        api.gemv_bf16(x, w, o, api.MODE_SILU)
+        g, u = ref[:, :half], ref[:, half:]
+        close(o, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gemv silu")
+
+
+def test_gemv_refuses_what_it_cannot_do():
+    x, w = rnd(65, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
+    with pytest.raises(api.KernelError):
+        api.gemv_bf16(x, w, torch.empty(65, 32, dtype=torch.bfloat16, device=DEV))
+    x, w = rnd(2, 12, dtype=torch.bfloat16), rnd(32, 12, dtype=torch.bfloat16)
+    with pytest.raises(api.KernelError):
+        api.gemv_bf16(x, w, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(api.KernelError):
+        api.attention_prefill_bf16(rnd(1, 24, dtype=torch.bfloat16), rnd(1, 24, dtype=torch.bfloat16), None, None,
+                                   torch.zeros(1, 2, dtype=torch.int32, device=DEV),
+                                   torch.zeros(2, dtype=torch.int32, device=DEV), torch.zeros(1, dtype=torch.int32, device=DEV),
+                                   torch.zeros(1, 1, dtype=torch.int32, device=DEV), 1, 1, 24, 0, 1.0)
+
+
+@pytest.mark.parametrize("V", [50, 4096, 151936])
+def test_sampler_greedy_and_gumbel(V):
+    n = 5
+    logits = rnd(n, V, seed=23, scale=2.0)
+    logits[1, 7] = logits[1, V - 1] = 50.0                           # a tie: the lowest index wins
+    chunks = api.sample_chunks(V)
+    ws_v, ws_i = torch.empty(n * chunks, device=DEV), torch.empty(n * chunks, dtype=torch.int32, device=DEV)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    temps = torch.zeros(n, device=DEV)
+    seeds = torch.zeros(n, 2, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([3, 9, -1, 0, 100], dtype=torch.int32, device=DEV)
+    api.sample(logits, temps, seeds, pos, None, ws_v, ws_i, out)
+    ref = logits.argmax(-1).tolist()
+    ref[1], ref[2] = 7, 0                                            # tie; padding row
+    assert out.tolist() == ref and pos.tolist() == [3, 9, -1, 0, 100]
+    api.sample(logits, temps, seeds, pos, None, ws_v, ws_i, out, advance=True)
+    assert pos.tolist() == [4, 10, -1, 1, 101]
+    if V > 5000:
+        return
+    # temperature: the kernel's choice is the plain Gumbel-max choice for (seed, position + 1)
+    temps[:] = 0.7
+    seed64 = [0x123456789ABCDEF0 + 977 * b for b in range(n)]
+    from dryft_challenge_htn_2026_b200.sampling import seed_words
+    seeds.copy_(torch.tensor([seed_words(s) for s in seed64], dtype=torch.int32))
+    pos = torch.tensor([3, 9, 20, 0, 100], dtype=torch.int32, device=DEV)
+    api.sample(logits, temps, seeds, pos, None, ws_v, ws_i, out)
+    for b in range(n):
+        want, z = plain.gumbel_argmax(logits[b].cpu(), 0.7, seed64[b], int(pos[b]) + 1)
+        got = int(out[b])
+        assert got == want or abs(z[got] - z[want]) < 1e-4, (b, got, want)
+    # same seed, other position: other draws; frequencies follow softmax(logits / T)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]], device=DEV).repeat(4000, 1).contiguous()
+    t4, s4 = torch.full((4000,), 1.0, device=DEV), torch.zeros(4000, 2, dtype=torch.int32, device=DEV)
+    p4 = torch.arange(4000, dtype=torch.int32, device=DEV)
+    o4 = torch.empty(4000, dtype=torch.int32, device=DEV)
+    api.sample(small, t4, s4, p4, None, torch.empty(4000, device=DEV), torch.empty(4000, dtype=torch.int32, device=DEV), o4)
+    freq = torch.bincount(o4.long(), minlength=4).float() / 4000
+    assert float((freq.cpu() - torch.softmax(small[0].cpu(), 0)).abs().max()) < 0.03
