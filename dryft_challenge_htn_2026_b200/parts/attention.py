@@ -81,7 +81,7 @@ class GQAAttention(Part):
             api.attention_generic(q, o, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, nh, nkv, hd, window, s.scale)
         elif ctx.is_decode:
             nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
-            ws_acc, ws_ml = ctx.scratch(("attn_decode", nh, hd, nsplit),
+            ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
                                         lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, a.device))
             api.attention_decode_bf16(q, o, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window, s.scale, nsplit,
                                       ws_acc, ws_ml)

@@ -112,7 +112,7 @@ def test_gated_mlp_part(dtype):
     if dtype == torch.bfloat16:
         t = {k: v.to(dtype).float() for k, v in t.items()}
     a = rnd(11, 72, seed=33).to(dtype)
-    ref = plain.gated_mlp(a.float(), {"mlp." + k: v for k, v in t.items()}, "mlp.")
+    ref = plain.gated_mlp(a.float(), {"mlp." + k: v for k, v in t.items()}, "")
     close(part.forward(None, a.to(DEV)), ref, dtype, "GatedMLP")
 
 
