@@ -43,7 +43,17 @@ def _lib(source, defines=None):
     return lib
 
 
-def _check(lib, err, what):
+_launches = 0
+
+
+def launch_count():
+    """Kernels of this library launched so far through these wrappers (library products not counted)."""
+    return _launches
+
+
+def _check(lib, err, what, kernels=1):
+    global _launches
+    _launches += kernels
     if err != 0:
         msg = lib.dk_error_string(err).decode()
         raise KernelError(f"{what}: CUDA error {err} ({msg})")
@@ -203,7 +213,8 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
     lib = _attn_lib(head_dim)
     _check(lib, lib.dk_attn_decode_bf16(_p(q), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos),
                                         _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
-                                        int(window or 0), c_float(scale), nsplit, _stream()), "attention_decode_bf16")
+                                        int(window or 0), c_float(scale), nsplit, _stream()), "attention_decode_bf16",
+           2 if nsplit > 1 else 1)
 
 
 # ---------------------------------------------------------------------------------------- products
@@ -277,4 +288,4 @@ def sample(logits, temperature, seeds, pos, rows, ws_val, ws_idx, out_tok, advan
     if ws_val.numel() < need or ws_idx.numel() < need:
         raise KernelError("sample: scratch too small")
     _check(lib, lib.dk_sample(_p(logits), n, V, _p(temperature), _p(seeds), _p(pos), _p(rows), _p(ws_val), _p(ws_idx),
-                              _p(out_tok), int(bool(advance)), _stream()), "sample")
+                              _p(out_tok), int(bool(advance)), _stream()), "sample", 2)
