@@ -44,8 +44,9 @@ def lib_path(source, defines=None):
     defines = dict(defines or {})
     with open(os.path.join(HERE, source), "rb") as f:
         text = f.read()
-    with open(os.path.join(HERE, "common.cuh"), "rb") as f:
-        text += f.read()
+    for header in sorted(n for n in os.listdir(HERE) if n.endswith((".cuh", ".h"))):
+        with open(os.path.join(HERE, header), "rb") as f:
+            text += f.read()
     tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items()))
     h = hashlib.sha1(text + repr((ARCH_FLAGS, NVCC_FLAGS, sorted(defines.items()))).encode()).hexdigest()[:12]
     stem = os.path.splitext(source)[0]
