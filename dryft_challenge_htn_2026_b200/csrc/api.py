@@ -86,6 +86,33 @@ def _need(t, name, dtype=None, dim=None):
         raise KernelError(f"{name} must have {dim} dimensions, got shape {tuple(t.shape)}")
 
 
+class Partial:
+    """The output of a split-K product that has not been added up yet: float32 [slices, rows,
+    cols]; the true value is the sum over slices. ``add_rmsnorm`` and ``qk_norm_rope_write`` take
+    it in place of a tensor and add the slices up while they read; anything else calls ``sum()``."""
+
+    def __init__(self, ws):
+        self.ws = ws
+
+    @property
+    def shape(self):
+        return self.ws.shape[1:]
+
+    def sum(self, dtype=torch.bfloat16):
+        out = torch.empty(self.shape, dtype=torch.bfloat16, device=self.ws.device)
+        lib = _lib("gemm.cu")
+        _check(lib, lib.dk_sum_partials(_p(self.ws), _p(out), c_longlong(out.numel()), self.ws.shape[0], _stream()),
+               "sum_partials")
+        return out.to(dtype)
+
+
+def _parts(x):
+    """(tensor or None, partial pointer, slices, stride) of an argument that may be a Partial."""
+    if isinstance(x, Partial):
+        return None, _p(x.ws), x.ws.shape[0], c_longlong(x.ws.shape[1] * x.ws.shape[2])
+    return x, c_void_p(0), 0, c_longlong(0)
+
+
 # ------------------------------------------------------------------------------------ row kernels
 def embed_rmsnorm(tok, embed, norm_w, eps, h_out, a_out):
     """h_out[t] = embed[tok[t]] (float32); a_out[t] = rmsnorm(h_out[t]) * norm_w."""
@@ -100,12 +127,13 @@ def embed_rmsnorm(tok, embed, norm_w, eps, h_out, a_out):
 def add_rmsnorm(h, delta, norm_w, eps, a_out, rows=None):
     """h += delta (delta may be None); a_out = rmsnorm(h) * norm_w. With ``rows`` (int32 indices)
     only those rows are normalised into a_out[0..len(rows)) and h is left unchanged."""
+    delta, parts, n_parts, stride = _parts(delta)
     _need(h, "h", torch.float32, 2), _need(delta, "delta", a_out.dtype, 2), _need(norm_w, "norm_w", torch.float32, 1)
     _need(rows, "rows", torch.int32, 1), _need(a_out, "a_out", None, 2)
     lib = _lib("elementwise.cu")
     n = h.shape[0] if rows is None else rows.numel()
-    _check(lib, lib.dk_add_rmsnorm(_dt(a_out), _p(h), _p(delta), _p(rows), _p(norm_w), c_float(eps), n, h.shape[1],
-                                   _p(a_out), _stream()), "add_rmsnorm")
+    _check(lib, lib.dk_add_rmsnorm(_dt(a_out), _p(h), _p(delta), parts, n_parts, stride, _p(rows), _p(norm_w),
+                                   c_float(eps), n, h.shape[1], _p(a_out), _stream()), "add_rmsnorm")
 
 
 def silu_mul(gu, out):
@@ -126,20 +154,22 @@ def qk_norm_rope_write(qkv, q_out, q_norm_w, k_norm_w, cos, sin, row_pos, row_se
     """Per-head RMSNorm (weights may be None), rotate-half rotation (cos/sin [positions, hd/2]
     float32, may be None), q to q_out [T, nh*hd], k and v into the paged stores
     [pages, n_kv, PAGE, hd] at each token's position. Rows with position < 0 are skipped."""
-    _need(qkv, "qkv", None, 2), _need(q_out, "q_out", qkv.dtype, 2)
+    width, n_tok = qkv.shape[1], qkv.shape[0]
+    qkv, parts, n_parts, stride = _parts(qkv)
+    _need(qkv, "qkv", q_out.dtype, 2), _need(q_out, "q_out", None, 2)
     _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
     _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
     _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
-    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", qkv.dtype), _need(v_store, "v_store", qkv.dtype)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", q_out.dtype), _need(v_store, "v_store", q_out.dtype)
     if head_dim % 2 or head_dim > 256:
         raise KernelError(f"head size {head_dim} not supported: even, at most 256")
-    if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
-        raise KernelError(f"qkv width {qkv.shape[1]} != (nh + 2 nkv) * hd")
+    if width != (n_heads + 2 * n_kv_heads) * head_dim:
+        raise KernelError(f"qkv width {width} != (nh + 2 nkv) * hd")
     lib = _lib("elementwise.cu")
-    _check(lib, lib.dk_qk_norm_rope_write(_dt(qkv), _p(qkv), _p(q_out), _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin),
-                                          _p(row_pos), _p(row_seq), _p(page_table), page_table.shape[1], _p(k_store),
-                                          _p(v_store), qkv.shape[0], n_heads, n_kv_heads, head_dim, c_float(eps),
-                                          int(bool(write_kv)), _stream()), "qk_norm_rope_write")
+    _check(lib, lib.dk_qk_norm_rope_write(_dt(q_out), _p(qkv), parts, n_parts, stride, _p(q_out), _p(q_norm_w),
+                                          _p(k_norm_w), _p(cos), _p(sin), _p(row_pos), _p(row_seq), _p(page_table),
+                                          page_table.shape[1], _p(k_store), _p(v_store), n_tok, n_heads, n_kv_heads,
+                                          head_dim, c_float(eps), int(bool(write_kv)), _stream()), "qk_norm_rope_write")
 
 
 # -------------------------------------------------------------------------------------- attention
@@ -180,14 +210,12 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=32, target_blocks=296):
-    """Number of key splits for decode attention: enough blocks to fill the GPU, fixed for a batch
-    size (it must not depend on sequence lengths, which change under a captured graph)."""
+def decode_splits(n_seq, n_kv_heads, group, max_splits=32, resident_blocks=3 * 148):
+    """Number of key splits for decode attention: as many as keep all blocks resident at once
+    (three per SM), fixed for a batch size (it must not depend on sequence lengths, which change
+    under a captured graph)."""
     blocks = n_seq * n_kv_heads * ((group + 15) // 16)
-    n = 1
-    while n < max_splits and blocks * n < target_blocks:
-        n *= 2
-    return n
+    return max(1, min(max_splits, resident_blocks // blocks))
 
 
 def attention_decode_ws(n_seq, n_heads, head_dim, nsplit, device):
@@ -233,40 +261,54 @@ def sgemm(x, w, out, mode=MODE_STORE):
     _check(lib, lib.dk_sgemm(_p(x), _p(w), _p(out), M, N, K, mode, _stream()), "sgemm")
 
 
-def gemv_plan(M, N, K, mode):
-    """(R, KS): weight-row tiles and K slices per block. Enough blocks to cover the GPU's 148 SMs
-    about twice when the matrix allows it, and no more warps than the register file holds."""
-    max_warps = 16 if M <= 16 else 8
-    tiles = (N + 15) // 16
-    chunks = (K + 31) // 32
-    if mode == MODE_SILU:
-        ks = max_warps // 2
-        while ks > 1 and chunks < 8 * ks:
-            ks //= 2
-        return 2, ks
-    r = 1
-    while r < max_warps and tiles // (r * 2) >= 296:
-        r *= 2
-    ks = max_warps // r
-    while ks > 1 and chunks < 8 * ks:
-        ks //= 2
-    return r, ks
+SM_COUNT = 148
+GEMV_BLOCKS_PER_SM = {1: 2, 2: 2, 4: 1, 8: 1}   # by 8-row batch tiles: what the kernel's registers allow at 8 warps
 
 
-def gemv_bf16(x, w, out, mode=MODE_STORE, plan=None):
-    """Skinny bfloat16 product for at most 64 rows of x; out bfloat16 (modes 0, 2) or float32 (1)."""
+def _batch_tiles(M):
+    return 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
+
+
+def gemv_plan(M, N, K, mode, allow_partial=False):
+    """(SK, warps, max_blocks). Every warp streams one unit (16 weight rows x one slice of K) on
+    its own; SK slices per tile are chosen so that all units fit on the GPU at once (one wave of
+    equal units is balanced by the memory system itself) with at least 4 chunks of 64 per slice."""
+    warps = 8
+    max_blocks = SM_COUNT * GEMV_BLOCKS_PER_SM[_batch_tiles(M)]
+    tiles, chunks = (N + 15) // 16, (K + 63) // 64
+    sk = 1
+    if allow_partial and mode != MODE_SILU:
+        while sk < 16 and tiles * sk * 2 <= max_blocks * warps and chunks >= 4 * sk * 2:
+            sk *= 2
+    return sk, warps, max_blocks
+
+
+def gemv_bf16(x, w, out=None, mode=MODE_STORE, plan=None):
+    """Skinny bfloat16 product for at most 64 rows of x. Returns ``out`` [M, N] (bfloat16 for
+    modes 0 and 2, float32 for mode 1), or, when the plan splits K (plan[0] > 1), a ``Partial``."""
     _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
     M, K = x.shape
-    N = out.shape[1]
+    N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
     if M > GEMV_MAX_ROWS or K % 8:
         raise KernelError(f"gemv_bf16: {M} rows (max {GEMV_MAX_ROWS}) / inner size {K} (multiple of 8) not supported")
-    if w.shape != ((2 * N if mode == MODE_SILU else N), K) or out.shape[0] != M:
-        raise KernelError(f"gemv_bf16: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
-    if out.dtype != (torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16):
-        raise KernelError(f"gemv_bf16: out dtype {out.dtype} does not fit mode {mode}")
-    r, ks = plan or gemv_plan(M, N, K, mode)
+    if w.shape[1] != K:
+        raise KernelError(f"gemv_bf16: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
+    sk, warps, max_blocks = plan or gemv_plan(M, N, K, mode)
+    ws = None
+    if sk > 1:
+        if mode == MODE_SILU:
+            raise KernelError("gemv_bf16: the SiLU epilogue cannot be split over K")
+        ws = torch.empty((sk, M, N), dtype=torch.float32, device=x.device)
+    else:
+        want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
+        if out is None:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        elif out.dtype != want or tuple(out.shape) != (M, N):
+            raise KernelError(f"gemv_bf16: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
     lib = _lib("gemm.cu")
-    _check(lib, lib.dk_gemv_bf16(_p(x), _p(w), _p(out), M, N, K, mode, r, ks, _stream()), "gemv_bf16")
+    _check(lib, lib.dk_gemv_bf16(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, warps, max_blocks, _stream()),
+           "gemv_bf16")
+    return Partial(ws) if sk > 1 else out
 
 
 # ---------------------------------------------------------------------------------------- sampling
@@ -289,3 +331,65 @@ def sample(logits, temperature, seeds, pos, rows, ws_val, ws_idx, out_tok, advan
         raise KernelError("sample: scratch too small")
     _check(lib, lib.dk_sample(_p(logits), n, V, _p(temperature), _p(seeds), _p(pos), _p(rows), _p(ws_val), _p(ws_idx),
                               _p(out_tok), int(bool(advance)), _stream()), "sample", 2)
+
+
+# ------------------------------------------------------------------------------------- L2 prefetch
+def l2_prefetch(t, stream=None):
+    """Hints the whole tensor into L2 from ``stream`` (default: the current stream)."""
+    lib = _lib("elementwise.cu")
+    st = _stream() if stream is None else c_void_p(stream.cuda_stream)
+    _check(lib, lib.dk_l2_prefetch(_p(t), c_longlong(t.numel() * t.element_size()), st), "l2_prefetch")
+
+
+# ------------------------------------------------------------------- streaming product (M <= 16)
+STREAM_MAX_ROWS = 16
+STREAM_BUILD = None   # compile-time overrides of the kernel's stage size, ring depth and warp count (tuning)
+
+def stream_plan(M, N, K, mode, allow_partial=False):
+    """(SK, blocks) for gemv_stream, or None if it cannot take the shape. Two persistent blocks
+    per SM; K is cut into the fewest slices that keep a block's piece of x in shared memory (2560
+    elements), and further (if the caller takes partial sums) while there are fewer than two
+    tiles per block (more slices cost the consumer more partial sums to add)."""
+    blocks = 2 * SM_COUNT
+    sk = 1
+    while ((K + sk - 1) // sk + 15) // 16 * 16 > 2560:
+        sk *= 2
+    if sk > 1 and (mode == MODE_SILU or not allow_partial):
+        return None
+    if allow_partial and mode != MODE_SILU:
+        tiles = (N + 15) // 16
+        while sk < 8 and tiles * sk < 2 * blocks and K // (sk * 2) >= 512:
+            sk *= 2
+    return sk, blocks
+
+
+def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
+    """The weight-streaming skinny product (asynchronous copies into shared-memory rings,
+    tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Same results and
+    return convention as ``gemv_bf16``."""
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
+    M, K = x.shape
+    N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
+    if M > STREAM_MAX_ROWS or K % 16:
+        raise KernelError(f"gemv_stream: {M} rows (max {STREAM_MAX_ROWS}) / inner size {K} (multiple of 16) not supported")
+    if w.shape[1] != K:
+        raise KernelError(f"gemv_stream: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
+    sk, blocks = plan or stream_plan(M, N, K, mode) or (0, 0)
+    if sk < 1 or blocks < sk or ((K + sk - 1) // sk + 15) // 16 * 16 > 2560:
+        raise KernelError(f"gemv_stream: K = {K} in {sk} slices on {blocks} blocks is not supported "
+                          "(a slice holds at most 2560 elements, and there is a block per slice at least)")
+    ws = None
+    if sk > 1:
+        if mode == MODE_SILU:
+            raise KernelError("gemv_stream: the SiLU epilogue cannot be split over K")
+        ws = torch.empty((sk, M, N), dtype=torch.float32, device=x.device)
+    else:
+        want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
+        if out is None:
+            out = torch.empty((M, N), dtype=want, device=x.device)
+        elif out.dtype != want or tuple(out.shape) != (M, N):
+            raise KernelError(f"gemv_stream: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
+    lib = _lib("gemv_stream.cu", STREAM_BUILD)
+    _check(lib, lib.dk_gemv_stream(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, _stream()),
+           "gemv_stream")
+    return Partial(ws) if sk > 1 else out

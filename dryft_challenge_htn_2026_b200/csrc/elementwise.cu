@@ -38,8 +38,10 @@ __global__ void embed_rmsnorm_kernel(const int* tok, const T* __restrict__ embed
 // h[row] += delta[row] (if delta);  a[out_row] = rmsnorm(h[row]) * w.
 // With `rows` the kernel gathers: out_row = blockIdx.x, row = rows[blockIdx.x], and h is not
 // written back (used for the final norm at the positions whose logits are wanted).
+// ``parts``: n_parts float32 partial sums [n_parts][rows of h][H] (the split-K output of the skinny
+// product) that are added up in order and then added to h like delta.
 template <typename T>
-__global__ void add_rmsnorm_kernel(float* h, const T* delta,
+__global__ void add_rmsnorm_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride,
                                    const int* rows, const float* __restrict__ w, float eps,
                                    int H, T* a) {
     __shared__ float red[33];
@@ -54,6 +56,11 @@ __global__ void add_rmsnorm_kernel(float* h, const T* delta,
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = hr[i];
         if (dr) v += to_f(dr[i]);
+        if (parts) {
+            float d = 0.f;
+            for (int k = 0; k < n_parts; k++) d += parts[(size_t)k * part_stride + row * H + i];
+            v += d;
+        }
         if (rows) vals[i] = v; else hr[i] = v;
         ss += v * v;
     }
@@ -84,8 +91,10 @@ __global__ void silu_mul_kernel(const T* gu, T* out, size_t n, int I) {
 // q goes to q_out [T, nh*hd]; k and v go to the token's place in the paged cache (unless
 // write_kv == 0, for a layer that reads another layer's keys and values).
 // Tokens with position < 0 are padding: nothing is written for them.
+// With ``parts`` the projection row is the sum of n_parts float32 partial rows
+// parts[k][t][heads*hd] (split-K output of the skinny product) instead of qkv[t].
 template <typename T>
-__global__ void qk_norm_rope_write_kernel(const T* qkv, T* q_out,
+__global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int n_parts, size_t part_stride, T* q_out,
                                           const float* __restrict__ qn, const float* __restrict__ kn,
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           const int* row_pos, const int* row_seq,
@@ -102,7 +111,13 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, T* q_out,
     const int pos = row_pos[t];
     if (pos < 0) return;
     const int half = hd >> 1;
-    const T* x = qkv + (size_t)t * heads * hd + (size_t)hidx * hd;
+    const size_t x_off = (size_t)t * heads * hd + (size_t)hidx * hd;
+    auto xin = [&](int d) {
+        if (parts == nullptr) return to_f(qkv[x_off + d]);
+        float s = 0.f;
+        for (int k = 0; k < n_parts; k++) s += parts[(size_t)k * part_stride + x_off + d];
+        return s;
+    };
 
     T* dst;
     if (hidx < nh) {
@@ -115,7 +130,7 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, T* q_out,
         dst = store + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
     }
     if (hidx >= nh + nkv) {  // value head: plain copy
-        for (int d = lane; d < hd; d += 32) dst[d] = x[d];
+        for (int d = lane; d < hd; d += 32) dst[d] = from_f<T>(xin(d));
         return;
     }
     // pairs (d, d + half), d = lane + 32*i; hd <= 256 gives at most 4 pairs a lane
@@ -124,8 +139,8 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, T* q_out,
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int d = lane + 32 * i;
-        x1[i] = d < half ? to_f(x[d]) : 0.f;
-        x2[i] = d < half ? to_f(x[d + half]) : 0.f;
+        x1[i] = d < half ? xin(d) : 0.f;
+        x2[i] = d < half ? xin(d + half) : 0.f;
         ss += x1[i] * x1[i] + x2[i] * x2[i];
     }
     const float* nw = hidx < nh ? qn : kn;
@@ -181,15 +196,16 @@ DK_EXPORT int dk_embed_rmsnorm(int dtype, const int* tok, const void* embed, con
                                        (const T*)embed, w, eps, H, V, h, (T*)a));
 }
 
-DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const int* rows, const float* w, float eps,
-                             int n_rows, int H, void* a, cudaStream_t st) {
+DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float* parts, int n_parts,
+                             long long part_stride, const int* rows, const float* w, float eps, int n_rows, int H,
+                             void* a, cudaStream_t st) {
     size_t smem = rows ? (size_t)H * sizeof(float) : 0;
     if (smem > 48 * 1024) {
         DISPATCH_T(dtype, cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                (int)smem));
     }
     DISPATCH_T(dtype, return dk_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(row_threads(H)), smem, st, h,
-                                       (const T*)delta, rows, w, eps, H, (T*)a));
+                                       (const T*)delta, parts, n_parts, (size_t)part_stride, rows, w, eps, H, (T*)a));
 }
 
 DK_EXPORT int dk_silu_mul(int dtype, const void* gu, void* out, long long n_rows, int I, cudaStream_t st) {
@@ -198,7 +214,8 @@ DK_EXPORT int dk_silu_mul(int dtype, const void* gu, void* out, long long n_rows
                                        (const T*)gu, (T*)out, n, I));
 }
 
-DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, const float* qn, const float* kn,
+DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* parts, int n_parts, long long part_stride,
+                                    void* q_out, const float* qn, const float* kn,
                                     const float* cos_t, const float* sin_t, const int* row_pos, const int* row_seq,
                                     const int* page_table, int pt_stride, void* k_store, void* v_store, int n_tok,
                                     int nh, int nkv, int hd, float eps, int write_kv, cudaStream_t st) {
@@ -206,10 +223,32 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, void* q_out, con
     long long warps = (long long)n_tok * (nh + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
     DISPATCH_T(dtype, return dk_launch(qk_norm_rope_write_kernel<T>, dim3(blocks), dim3(128), 0, st, (const T*)qkv,
-                                       (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
+                                       parts, n_parts, (size_t)part_stride, (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
                                        (T*)k_store, (T*)v_store, n_tok, nh, nkv, hd, eps, write_kv));
 }
 
 DK_EXPORT int dk_gather_rows_f32(const float* src, const int* rows, float* out, int n_rows, int H, cudaStream_t st) {
     return dk_launch(gather_rows_f32_kernel, dim3(n_rows), dim3(256), 0, st, src, rows, out, H);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Asks the memory system to bring [p, p + bytes) into L2 (a hint; nothing is read into the SM).
+// Launched beside small latency-bound kernels of the decode step so that HBM keeps streaming the
+// next weight matrix while they run.
+__global__ void l2_prefetch_kernel(const char* p, size_t bytes, size_t piece) {
+    const size_t n = (bytes + piece - 1) / piece;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t off = i * piece;
+        const unsigned sz = (unsigned)(bytes - off < piece ? (bytes - off) & ~(size_t)15 : piece);
+        if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"(sz) : "memory");
+    }
+}
+
+DK_EXPORT int dk_l2_prefetch(const void* p, long long bytes, cudaStream_t st) {
+    if (bytes <= 0) return 0;
+    const size_t piece = 16384;
+    size_t n = ((size_t)bytes + piece - 1) / piece;
+    unsigned blocks = (unsigned)((n + 127) / 128);
+    if (blocks > 148) blocks = 148;
+    return dk_launch(l2_prefetch_kernel, dim3(blocks), dim3(128), 0, st, (const char*)p, (size_t)bytes, piece);
 }

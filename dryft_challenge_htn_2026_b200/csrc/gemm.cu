@@ -80,14 +80,6 @@ DK_EXPORT int dk_sgemm(const float* x, const float* W, float* out, int M, int N,
 }
 
 // -------------------------------------------------------------------------------------- gemv_bf16
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
-
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -96,126 +88,193 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-#define GV_U 4  // 32-element chunks of K a thread has in flight per batch (2 x 16 B each)
-
-// Warp (r, ks) of a block owns 16 weight rows (tile blockIdx.x*R + r; in mode 2 r selects gate or
-// up) and the ks-th slice of K. Within a 32-element chunk of K, lane (g, t) loads the 8 elements
-// 8t..8t+7 of rows g and g+8 (one 16-byte load each) and the same 8 elements of x row nt*8+g; the
-// two mma steps of the chunk use elements {0..3} and {4..7} of each lane's 8, which permutes K
-// identically for both operands.
-template <int MT, int MODE>
-__global__ void gemv_bf16_kernel(const bf16* x, const bf16* __restrict__ W, void* out,
-                                 int M, int N, int K, int R, int KS) {
-    extern __shared__ float red[];  // [warps][16][8*MT]
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int r = warp / KS, ks = warp % KS;
-    const int tile = MODE == 2 ? blockIdx.x : blockIdx.x * R + r;
-    const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
-    const bool v_lo = n_lo < N, v_hi = n_hi < N;
-    const size_t w_row0 = MODE == 2 ? (size_t)r * N : 0;
-    const bf16* wlo = W + (w_row0 + (v_lo ? n_lo : 0)) * (size_t)K + 8 * t;
-    const bf16* whi = W + (w_row0 + (v_hi ? n_hi : 0)) * (size_t)K + 8 * t;
-    const int C = (K + 31) >> 5;
-    const int cps = (C + KS - 1) / KS;
-    const int c_begin = ks * cps, c_end = min(C, c_begin + cps);
-
-    float acc[MT][4];
+// Streaming weight load of NW 32-bit words (4: 16 bytes, 8: 32 bytes in one instruction), not
+// kept in L1; `words` of them are inside the matrix (the rest read as zero).
+template <int NW>
+__device__ __forceinline__ void ld_weights(uint32_t (&r)[NW], const bf16* p, int words) {
+    if (NW == 8 && words >= 8) {
+        asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4 % NW]), "=r"(r[5 % NW]),
+                       "=r"(r[6 % NW]), "=r"(r[7 % NW])
+                     : "l"(p));
+        return;
+    }
 #pragma unroll
-    for (int i = 0; i < MT; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int i = 0; i < NW; i++) r[i] = 0u;
+    if (words >= 4)
+        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                     : "l"(p));
+}
 
-    uint4 wl[2][GV_U], wh[2][GV_U];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    auto load = [&](int buf, int c0) {
+// Activation load (plain, coherent: the previous kernel wrote it).
+template <int NW>
+__device__ __forceinline__ void ld_acts(uint32_t (&r)[NW], const bf16* p, int words) {
 #pragma unroll
-        for (int u = 0; u < GV_U; u++) {
-            const int c = c0 + u;
-            const bool ok = c < c_end && (c * 32 + 8 * t) < K;
-            wl[buf][u] = (ok && v_lo) ? ldg_stream(wlo + (size_t)c * 32) : zero;
-            wh[buf][u] = (ok && v_hi) ? ldg_stream(whi + (size_t)c * 32) : zero;
+    for (int i = 0; i < NW; i += 4) {
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (words >= i + 4) v = *reinterpret_cast<const uint4*>(p + 2 * i);
+        r[i] = v.x, r[i + 1] = v.y, r[i + 2] = v.z, r[i + 3] = v.w;
+    }
+}
+
+// Every warp works alone on units (tile of 16 weight rows, slice of K); no shared memory, no
+// block-wide synchronisation. With SK slices per tile the warps write float32 partial sums
+// ws[slice][m][n] that the consuming kernel adds up in slice order (a fixed order: results do not
+// depend on timing); with SK == 1 they write the result itself. Mode 2 (SiLU gate/up) needs
+// SK == 1: a unit is the gate tile and the up tile of the same 16 outputs.
+// K is walked in chunks of 8*NW elements: lane (g, t) loads the 2*NW elements
+// [2*NW*t, 2*NW*(t+1)) of the chunk for rows g and g+8 (one instruction each; with NW = 8 the four
+// lanes of a row cover a whole 128-byte line) and the same elements of x row nt*8+g. mma step s of
+// the chunk uses words 2s and 2s+1 of every lane, which permutes K identically for both operands.
+// NW = 8 needs K % 16 == 0 (32-byte aligned rows). Units are numbered slice-fastest, so the
+// warps of a block stream neighbouring addresses.
+template <int MT, int MODE, int NW>
+__global__ void __launch_bounds__(256)
+gemv_bf16_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK,
+                 int units) {
+    constexpr int CH = 8 * NW;               // elements of K per chunk
+    constexpr int EPT = 2 * NW;              // elements per lane per chunk
+    constexpr int ROWS = MODE == 2 ? 4 : 2;  // weight rows a lane streams: (g, g+8) of gate [and of up]
+    constexpr int U = MODE == 2 ? 1 : 2;     // chunks per batch; two batches are in flight
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int wpc = blockDim.x >> 5;
+    const int C = (K + CH - 1) / CH;
+    const int cps = (C + SK - 1) / SK;
+    bool waited = false;
+    for (int u = blockIdx.x * wpc + (threadIdx.x >> 5); u < units; u += gridDim.x * wpc) {
+        const int tile = u / SK, slice = u % SK;
+        const int c_begin = slice * cps, c_end = min(C, c_begin + cps);
+        const int n_lo = tile * 16 + g, n_hi = n_lo + 8;
+        const bool v_lo = n_lo < N, v_hi = n_hi < N;
+        const bf16* wrow[ROWS];
+        wrow[0] = W + (size_t)(v_lo ? n_lo : 0) * K + EPT * t;
+        wrow[1] = W + (size_t)(v_hi ? n_hi : 0) * K + EPT * t;
+        if (MODE == 2) {
+            wrow[2 % ROWS] = wrow[0] + (size_t)N * K;
+            wrow[3 % ROWS] = wrow[1] + (size_t)N * K;
         }
-    };
-    auto consume = [&](int buf, int c0) {
+        float acc[MODE == 2 ? 2 : 1][MT][4];
 #pragma unroll
-        for (int u = 0; u < GV_U; u++) {
-            const int c = c0 + u;
-            const bool ok = c < c_end && (c * 32 + 8 * t) < K;
+        for (int h = 0; h < (MODE == 2 ? 2 : 1); h++)
 #pragma unroll
-            for (int nt = 0; nt < MT; nt++) {
-                const int m = nt * 8 + g;
-                uint4 xr = zero;
-                if (ok && m < M) xr = *reinterpret_cast<const uint4*>(x + (size_t)m * K + c * 32 + 8 * t);
-                mma16816(acc[nt], wl[buf][u].x, wh[buf][u].x, wl[buf][u].y, wh[buf][u].y, xr.x, xr.y);
-                mma16816(acc[nt], wl[buf][u].z, wh[buf][u].z, wl[buf][u].w, wh[buf][u].w, xr.z, xr.w);
+            for (int i = 0; i < MT; i++) acc[h][i][0] = acc[h][i][1] = acc[h][i][2] = acc[h][i][3] = 0.f;
+
+        uint32_t wr[2][U][ROWS][NW];
+        auto words_at = [&](int c) {  // 32-bit words of this lane's part of chunk c that lie inside K
+            if (c >= c_end) return 0;
+            const int left = K - (c * CH + EPT * t);
+            return left <= 0 ? 0 : (left >= EPT ? NW : left / 2);
+        };
+        auto load = [&](int buf, int c0) {
+#pragma unroll
+            for (int uu = 0; uu < U; uu++) {
+                const int words = words_at(c0 + uu);
+#pragma unroll
+                for (int rr = 0; rr < ROWS; rr++)
+                    ld_weights<NW>(wr[buf][uu][rr], wrow[rr] + (size_t)(c0 + uu) * CH, ((rr & 1) ? v_hi : v_lo) ? words : 0);
+            }
+        };
+        auto consume = [&](int buf, int c0) {
+#pragma unroll
+            for (int uu = 0; uu < U; uu++) {
+                const int words = words_at(c0 + uu);
+#pragma unroll
+                for (int nt = 0; nt < MT; nt++) {
+                    const int m = nt * 8 + g;
+                    uint32_t xr[NW];
+                    ld_acts<NW>(xr, x + (size_t)(m < M ? m : 0) * K + (size_t)(c0 + uu) * CH + EPT * t, m < M ? words : 0);
+#pragma unroll
+                    for (int s = 0; s < NW / 2; s++) {
+                        mma16816(acc[0][nt], wr[buf][uu][0][2 * s], wr[buf][uu][1][2 * s], wr[buf][uu][0][2 * s + 1],
+                                 wr[buf][uu][1][2 * s + 1], xr[2 * s], xr[2 * s + 1]);
+                        if (MODE == 2)
+                            mma16816(acc[MODE == 2 ? 1 : 0][nt], wr[buf][uu][2 % ROWS][2 * s], wr[buf][uu][3 % ROWS][2 * s],
+                                     wr[buf][uu][2 % ROWS][2 * s + 1], wr[buf][uu][3 % ROWS][2 * s + 1], xr[2 * s],
+                                     xr[2 * s + 1]);
+                    }
+                }
+            }
+        };
+
+        load(0, c_begin);  // weights do not depend on the previous kernel: in flight before the wait
+        load(1, c_begin + U);
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+        for (int c0 = c_begin; c0 < c_end; c0 += 2 * U) {
+            consume(0, c0);
+            load(0, c0 + 2 * U);
+            consume(1, c0 + U);
+            load(1, c0 + 3 * U);
+        }
+#pragma unroll
+        for (int nt = 0; nt < MT; nt++) {
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                const int m = nt * 8 + 2 * t + (c & 1);
+                const int n = (c & 2) ? n_hi : n_lo;
+                if (m >= M || n >= N) continue;
+                float v = acc[0][nt][c];
+                if (MODE == 2) v = v / (1.f + expf(-v)) * acc[MODE == 2 ? 1 : 0][nt][c];
+                if (SK > 1) ws[((size_t)slice * M + m) * N + n] = v;
+                else if (MODE == 1) reinterpret_cast<float*>(out)[(size_t)m * N + n] = v;
+                else reinterpret_cast<bf16*>(out)[(size_t)m * N + n] = __float2bfloat16_rn(v);
             }
         }
-    };
-
-    load(0, c_begin);  // weights do not depend on the previous kernel: in flight before the wait
-    pdl_wait();
-    for (int c0 = c_begin; c0 < c_end; c0 += 2 * GV_U) {
-        load(1, c0 + GV_U);
-        consume(0, c0);
-        load(0, c0 + 2 * GV_U);
-        consume(1, c0 + GV_U);
     }
+    if (!waited) pdl_wait();
     pdl_launch_dependents();
-
-    const int NB = 8 * MT;
-    float* mine = red + (size_t)warp * 16 * NB;
-#pragma unroll
-    for (int nt = 0; nt < MT; nt++) {
-        mine[g * NB + nt * 8 + 2 * t] = acc[nt][0];
-        mine[g * NB + nt * 8 + 2 * t + 1] = acc[nt][1];
-        mine[(g + 8) * NB + nt * 8 + 2 * t] = acc[nt][2];
-        mine[(g + 8) * NB + nt * 8 + 2 * t + 1] = acc[nt][3];
-    }
-    __syncthreads();
-    const int tiles_here = MODE == 2 ? 1 : R;
-    for (int idx = threadIdx.x; idx < tiles_here * NB * 16; idx += blockDim.x) {
-        const int i = idx & 15, j = (idx >> 4) % NB, rr = idx / (16 * NB);
-        const int n = (MODE == 2 ? blockIdx.x : blockIdx.x * R + rr) * 16 + i;
-        if (n >= N || j >= M) continue;
-        float s = 0.f;
-        for (int k = 0; k < KS; k++) s += red[((size_t)(rr * KS + k) * 16 + i) * NB + j];
-        if (MODE == 2) {
-            float u = 0.f;
-            for (int k = 0; k < KS; k++) u += red[((size_t)(KS + k) * 16 + i) * NB + j];
-            s = s / (1.f + expf(-s)) * u;
-        }
-        if (MODE == 1) reinterpret_cast<float*>(out)[(size_t)j * N + n] = s;
-        else reinterpret_cast<bf16*>(out)[(size_t)j * N + n] = __float2bfloat16_rn(s);
-    }
 }
 
-template <int MT, int MODE>
-static int launch_gemv(const bf16* x, const bf16* W, void* out, int M, int N, int K, int R, int KS, cudaStream_t st) {
-    const int warps = (MODE == 2 ? 2 : R) * KS;
-    const int tiles = (N + 15) / 16;
-    const unsigned blocks = MODE == 2 ? tiles : (tiles + R - 1) / R;
-    const size_t smem = (size_t)warps * 16 * 8 * MT * sizeof(float);
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(gemv_bf16_kernel<MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        attr_set = true;
-    }
-    return dk_launch(gemv_bf16_kernel<MT, MODE>, dim3(blocks), dim3(32 * warps), smem, st, x, W, out, M, N, K, R, KS);
+template <int MT, int MODE, int NW>
+static int launch_gemv(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int warps,
+                       int max_blocks, cudaStream_t st) {
+    const int units = ((N + 15) / 16) * SK;
+    int blocks = (units + warps - 1) / warps;
+    if (blocks > max_blocks) blocks = max_blocks;
+    return dk_launch(gemv_bf16_kernel<MT, MODE, NW>, dim3(blocks), dim3(32 * warps), 0, st, x, W, out, ws, M, N, K, SK,
+                     units);
 }
 
-// x [M,K] bf16, W [N,K] bf16 (mode 2: [2N,K]); R row tiles and KS K-slices per block, R*KS <= 32
-// (mode 2: 2*KS <= 32).
-DK_EXPORT int dk_gemv_bf16(const void* x, const void* W, void* out, int M, int N, int K, int mode, int R, int KS,
-                           cudaStream_t st) {
-    if (M < 1 || M > 64 || K % 8 != 0 || R < 1 || KS < 1 || (mode == 2 ? 2 : R) * KS > 32) return (int)cudaErrorInvalidValue;
+// x [M,K] bf16, W [N,K] bf16 (mode 2: [2N,K]). SK slices of K per 16-row tile; SK > 1 writes
+// float32 partial sums ws [SK][M][N] instead of out (modes 0 and 1 only). warps per block <= 8;
+// at most max_blocks blocks (warps loop over units beyond that).
+DK_EXPORT int dk_gemv_bf16(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
+                           int warps, int max_blocks, cudaStream_t st) {
+    if (M < 1 || M > 64 || K % 8 != 0 || SK < 1 || warps < 1 || warps > 8 || max_blocks < 1) return (int)cudaErrorInvalidValue;
+    if (SK > 1 && (mode == 2 || ws == nullptr)) return (int)cudaErrorInvalidValue;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-#define GV_CASE(MT)                                                                       \
-    if (mode == 0) return launch_gemv<MT, 0>(xp, wp, out, M, N, K, R, KS, st);            \
-    if (mode == 1) return launch_gemv<MT, 1>(xp, wp, out, M, N, K, R, KS, st);            \
-    return launch_gemv<MT, 2>(xp, wp, out, M, N, K, R, KS, st);
+    const bool wide = K % 16 == 0 && ((uintptr_t)W % 32 == 0);
+#define GV_MODE(MT, NW)                                                                                \
+    if (mode == 0) return launch_gemv<MT, 0, NW>(xp, wp, out, ws, M, N, K, SK, warps, max_blocks, st); \
+    if (mode == 1) return launch_gemv<MT, 1, NW>(xp, wp, out, ws, M, N, K, SK, warps, max_blocks, st); \
+    return launch_gemv<MT, 2, NW>(xp, wp, out, ws, M, N, K, SK, warps, max_blocks, st);
+#define GV_CASE(MT)              \
+    if (wide) { GV_MODE(MT, 8) } \
+    GV_MODE(MT, 4)
     if (M <= 8) { GV_CASE(1) }
     if (M <= 16) { GV_CASE(2) }
     if (M <= 32) { GV_CASE(4) }
     GV_CASE(8)
 #undef GV_CASE
+#undef GV_MODE
+}
+
+// out[m][n] = sum over slices of ws[slice][m][n], stored as bf16: for a consumer that cannot add
+// the partial sums up itself.
+__global__ void sum_partials_kernel(const float* ws, bf16* out, size_t mn, int SK) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= mn) return;
+    float s = 0.f;
+    for (int k = 0; k < SK; k++) s += ws[(size_t)k * mn + i];
+    out[i] = __float2bfloat16_rn(s);
+}
+
+DK_EXPORT int dk_sum_partials(const float* ws, void* out, long long mn, int SK, cudaStream_t st) {
+    return dk_launch(sum_partials_kernel, dim3((unsigned)((mn + 255) / 256)), dim3(256), 0, st, ws, (bf16*)out, (size_t)mn, SK);
 }

@@ -34,6 +34,8 @@ class CausalLM:
         self._entry_requests = [self.blocks[owners[c]].cache_requests() for c in range(n_entries)]
         self.embed = self.head = None
         self.tied = None
+        self.prefetch = False         # L2 prefetch of the next weight matrix during short decode kernels (side stream)
+        self._prefetcher = None
 
     # -- parameters --------------------------------------------------------------------------
     def param_decls(self, tied):
@@ -76,9 +78,22 @@ class CausalLM:
                 total += sum(v.numel() * v.element_size() for v in t.values() if isinstance(v, torch.Tensor))
         return total
 
+    def weights_in_order(self):
+        """The matrices one step streams, in the order of use (for the decode-step prefetcher)."""
+        out = []
+        for e in self.spec.schedule:
+            out += self.blocks[e.layer].weights_in_order()
+        return out + [self.head]
+
     # -- one step ----------------------------------------------------------------------------
     def forward(self, ctx, cache):
         s, rt = self.spec, self.rt
+        ctx.prefetcher = None
+        if self.prefetch and ctx.is_decode and rt.dtype == torch.bfloat16 and ctx.n_tok <= 64:
+            if self._prefetcher is None:
+                from .prefetch import WeightPrefetcher
+                self._prefetcher = WeightPrefetcher(self.weights_in_order())
+            ctx.prefetcher = self._prefetcher
         h = torch.empty((ctx.n_tok, s.hidden_size), dtype=torch.float32, device=rt.device)
         a = torch.empty((ctx.n_tok, s.hidden_size), dtype=rt.dtype, device=rt.device)
         first = self.blocks[s.schedule[0].layer]
@@ -89,8 +104,12 @@ class CausalLM:
         for i, e in enumerate(s.schedule):
             pending = self.blocks[e.layer].forward(ctx, h, pending, cache.views(e.cache), e.writes,
                                                    a if (i == 0 and fused) else None)
-        if ctx.n_want == 0:
-            return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
-        an = torch.empty((ctx.n_want, s.hidden_size), dtype=rt.dtype, device=rt.device)
-        self.final_norm.add_forward(h, pending, an, rows=ctx.want_rows)
-        return linear(an, self.head, STORE_F32)
+        try:
+            if ctx.n_want == 0:
+                return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
+            an = torch.empty((ctx.n_want, s.hidden_size), dtype=rt.dtype, device=rt.device)
+            self.final_norm.add_forward(h, pending, an, rows=ctx.want_rows)
+            return linear(an, self.head, STORE_F32)
+        finally:
+            if ctx.prefetcher is not None:
+                ctx.prefetcher.join()

@@ -51,6 +51,9 @@ class GQAAttention(Part):
             self.q_norm.bind({"weight": tensors.pop("q_norm.weight")})
             self.k_norm.bind({"weight": tensors.pop("k_norm.weight")})
 
+    def weights_in_order(self):
+        return [self.w_qkv, self.w_o]
+
     def cache_requests(self):
         s = self.spec
         return [KVRequest(s.num_kv_heads, s.head_dim, s.window, self.rt.dtype)]
@@ -64,12 +67,14 @@ class GQAAttention(Part):
         s, kv = self.spec, views[0]
         nh, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
         table = ctx.tables[kv.group]
-        qkv = linear(a, self.w_qkv)
+        qkv = linear(a, self.w_qkv, ctx=ctx, allow_partial=True)
         cos = sin = None
         if self.position is not None:
             if getattr(self.position, "fused_tables", False):
                 cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
             else:
+                if isinstance(qkv, api.Partial):
+                    qkv = qkv.sum(a.dtype)
                 self.position.apply(qkv, ctx, nh, nkv, hd)
         q = torch.empty((ctx.n_tok, nh * hd), dtype=a.dtype, device=a.device)
         api.qk_norm_rope_write(qkv, q, self.q_norm.weight if self.q_norm else None,
@@ -88,7 +93,7 @@ class GQAAttention(Part):
         else:
             api.attention_prefill_bf16(q, o, kv.k, kv.v, ctx.tiles, ctx.cu_q, ctx.seq_pos0, table, nh, nkv, hd,
                                        window, s.scale)
-        return linear(o, self.w_o)
+        return linear(o, self.w_o, ctx=ctx, allow_partial=True)
 
 
 register_part(AttentionSpec, GQAAttention)

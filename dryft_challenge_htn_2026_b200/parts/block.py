@@ -32,6 +32,13 @@ class PreNormBlock(Part):
         for attr, pre in self.SUB:
             getattr(self, attr).bind({k[len(pre):]: v for k, v in tensors.items() if k.startswith(pre)})
 
+    def weights_in_order(self):
+        out = []
+        for attr, _ in self.SUB:
+            fn = getattr(getattr(self, attr), "weights_in_order", None)
+            out += fn() if fn else []
+        return out
+
     def cache_requests(self):
         return self.mixer.cache_requests()
 

@@ -26,8 +26,11 @@ class GatedMLP(Part):
         self.w_gate_up = torch.cat([tensors.pop("gate_proj.weight"), tensors.pop("up_proj.weight")], 0).contiguous()
         self.w_down = tensors.pop("down_proj.weight").contiguous()
 
+    def weights_in_order(self):
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, ctx, a):
-        return linear(linear(a, self.w_gate_up, SILU), self.w_down)
+        return linear(linear(a, self.w_gate_up, SILU, ctx, gap_follows=False), self.w_down, ctx=ctx, allow_partial=True)
 
 
 register_part(GatedMLPSpec, GatedMLP)

@@ -10,19 +10,32 @@ from ..csrc import api
 STORE, STORE_F32, SILU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SILU
 
 
-def linear(x, w, mode=STORE):
+def linear(x, w, mode=STORE, ctx=None, gap_follows=True, allow_partial=False):
     """mode STORE: [M, N] in x's dtype; STORE_F32: float32 (logits); SILU: w = [gate; up] rows,
-    returns silu(x.gate^T) * (x.up^T) of width N/2."""
+    returns silu(x.gate^T) * (x.up^T) of width N/2. ``ctx``: the step context; when it carries a
+    weight prefetcher and short kernels follow this product (``gap_follows``), the next matrix is
+    hinted into L2 behind it. ``allow_partial``: the caller can take ``csrc.api.Partial`` (split-K
+    partial sums, added up by the kernel that consumes them) instead of a tensor."""
+    out = _linear(x, w, mode, allow_partial)
+    pf = getattr(ctx, "prefetcher", None)
+    if pf is not None and gap_follows:
+        pf.after(w)
+    return out
+
+
+def _linear(x, w, mode, allow_partial):
     M, K = x.shape
     N = w.shape[0] // 2 if mode == SILU else w.shape[0]
     if x.dtype == torch.float32:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         api.sgemm(x, w, out, mode)
         return out
+    if M <= api.STREAM_MAX_ROWS and K % 16 == 0:
+        plan = api.stream_plan(M, N, K, mode, allow_partial)
+        if plan is not None:
+            return api.gemv_stream(x, w, None, mode, plan)
     if M <= api.GEMV_MAX_ROWS:
-        out = torch.empty((M, N), dtype=torch.float32 if mode == STORE_F32 else torch.bfloat16, device=x.device)
-        api.gemv_bf16(x, w, out, mode)
-        return out
+        return api.gemv_bf16(x, w, None, mode, api.gemv_plan(M, N, K, mode, allow_partial))
     if mode == STORE_F32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     y = torch.mm(x, w.t())

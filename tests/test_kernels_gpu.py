@@ -265,15 +265,53 @@ def test_gemv_bf16(M, N, K):
     out32 = torch.empty(M, N, device=DEV)
     api.gemv_bf16(x, w, out32, api.MODE_STORE_F32)
     assert float((out32 - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))   # float32 accumulate and store
-    for plan in [(1, 1), (2, 2), (1, 8), (8, 1)]:
-        api.gemv_bf16(x, w, out32, api.MODE_STORE_F32, plan=plan)
-        assert float((out32 - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
+    # plans (slices of K per tile, warps per block, most blocks): split K gives partial sums, few
+    # blocks make the warps loop over units
+    for plan in [(1, 8, 296), (1, 3, 2), (2, 8, 296), (4, 1, 5), (16, 8, 1000)]:
+        r = api.gemv_bf16(x, w, None, api.MODE_STORE_F32, plan=plan)
+        if plan[0] > 1:
+            assert isinstance(r, api.Partial) and tuple(r.ws.shape) == (plan[0], M, N)
+            r = r.ws.sum(0)
+        assert float((r - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
+    close(api.gemv_bf16(x, w, None, api.MODE_STORE, plan=(4, 8, 296)).sum(), ref, torch.bfloat16, "summed partials")
     if N % 2 == 0:
         half = N // 2
         o = torch.empty(M, half, dtype=torch.bfloat16, device=DEV)
         api.gemv_bf16(x, w, o, api.MODE_SILU)
         g, u = ref[:, :half], ref[:, half:]
         close(o, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gemv silu")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_consumers_add_up_partial_sums(dtype):
+    """add_rmsnorm and qk_norm_rope_write given split-K partial sums equal the same kernels given the sum."""
+    T, H = 6, 200
+    parts = rnd(3, T, H, seed=40)
+    whole = parts.sum(0)
+    h0, w = rnd(T, H, seed=41), 1 + 0.1 * rnd(H, seed=42)
+    ha, hb = h0.clone(), h0.clone()
+    aa, ab = torch.empty(T, H, dtype=dtype, device=DEV), torch.empty(T, H, dtype=dtype, device=DEV)
+    api.add_rmsnorm(ha, api.Partial(parts), w, 1e-6, aa)
+    assert torch.allclose(ha, h0 + whole, atol=1e-5)
+    close(aa, rms(h0 + whole, w, 1e-6), dtype, "add_rmsnorm(partial)")
+    rows = torch.tensor([4, 1], dtype=torch.int32, device=DEV)
+    api.add_rmsnorm(hb, api.Partial(parts), w, 1e-6, ab, rows)
+    close(ab[:2], rms((h0 + whole)[rows.long()], w, 1e-6), dtype, "gathered add_rmsnorm(partial)")
+    nh, nkv, hd = 4, 2, 32
+    s = paged_setup([0, 10], [3, 3], nkv, hd, dtype, seed=43)
+    qparts = rnd(4, 6, (nh + 2 * nkv) * hd, seed=44)
+    qn, kn = 1 + 0.1 * rnd(hd, seed=45), 1 + 0.1 * rnd(hd, seed=46)
+    cos, sin = plain.rope_tables(1e4, hd, 64)
+    cos_h, sin_h = cos[:, :hd // 2].contiguous().to(DEV), sin[:, :hd // 2].contiguous().to(DEV)
+    outs = []
+    for arg in (api.Partial(qparts), qparts.sum(0).to(dtype)):
+        s["k_store"].zero_(), s["v_store"].zero_()
+        q_out = torch.empty(6, nh * hd, dtype=dtype, device=DEV)
+        api.qk_norm_rope_write(arg, q_out, qn, kn, cos_h, sin_h, s["row_pos"], s["row_seq"], s["table"], s["k_store"],
+                               s["v_store"], nh, nkv, hd, 1e-6)
+        outs.append((q_out.float(), s["k_store"].float().clone(), s["v_store"].float().clone()))
+    for a, b in zip(*outs):
+        close(a, b, dtype, "qk_norm_rope_write(partial)")
 
 
 def test_gemv_refuses_what_it_cannot_do():
@@ -328,3 +366,32 @@ def test_sampler_greedy_and_gumbel(V):
     api.sample(small, t4, s4, p4, None, torch.empty(4000, device=DEV), torch.empty(4000, dtype=torch.int32, device=DEV), o4)
     freq = torch.bincount(o4.long(), minlength=4).float() / 4000
     assert float((freq.cpu() - torch.softmax(small[0].cpu(), 0)).abs().max()) < 0.03
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(64, 64), (300, 96), (200, 2560), (2560, 2448), (100, 4096)])
+def test_gemv_stream(M, N, K):
+    """The streaming product against x.w^T: every mode, slices of K, few and many blocks."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=51), rnd(N, K, dtype=torch.bfloat16, seed=52, scale=0.05)
+    ref = x.float() @ w.float().T
+    if K <= 2560:
+        close(api.gemv_stream(x, w, None, api.MODE_STORE, (1, 296)), ref, torch.bfloat16, "stream store")
+    for plan in [(1, 1), (1, 5), (2, 296), (4, 7), (8, 296)]:
+        if (-(-K // plan[0]) + 15) // 16 * 16 > 2560:
+            with pytest.raises(api.KernelError):
+                api.gemv_stream(x, w, None, api.MODE_STORE_F32, plan)
+            continue
+        r = api.gemv_stream(x, w, None, api.MODE_STORE_F32, plan)
+        if plan[0] > 1:
+            assert isinstance(r, api.Partial) and tuple(r.ws.shape) == (plan[0], M, N)
+            r = r.ws.sum(0)
+        assert float((r - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
+    if N % 2 == 0 and K <= 2560:
+        half = N // 2
+        g, u = ref[:, :half], ref[:, half:]
+        close(api.gemv_stream(x, w, None, api.MODE_SILU, (1, 296)), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "stream silu")
+    # the plan the model uses
+    plan = api.stream_plan(M, N, K, api.MODE_STORE, allow_partial=True)
+    r = api.gemv_stream(x, w, None, api.MODE_STORE, plan)
+    close(r.sum() if isinstance(r, api.Partial) else r, ref, torch.bfloat16, "stream planned")
+    assert api.stream_plan(M, N, 9728, api.MODE_SILU) is None and api.stream_plan(M, N, 9728, api.MODE_STORE, True)[0] >= 4
