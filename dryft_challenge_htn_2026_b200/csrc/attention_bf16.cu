@@ -395,3 +395,241 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
     return dk_launch(attn_combine_kernel, dim3(n_seq * nh), dim3(HD < 128 ? HD : 128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, nsplit);
 }
+
+// ------------------------------------------------------------------------------- fused decode
+// One launch for a decode step's whole mixer core: per-head RMSNorm + rotation of the new token's
+// q and k, the cache write, attention over the cache split over the keys, and the merge of the
+// splits. grid (nsplit, nkv * mtiles, sequences) as attn_decode_kernel.
+//  * Every block normalises and rotates the query heads it owns and the new key of its kv head
+//    itself (a few hundred elements) from the projection row qkv[b] = [q | k | v], given either
+//    as a bf16 tensor or as n_parts float32 partial sums parts[k][b][width].
+//  * The block whose key range holds the new token's page patches its shared-memory copy of that
+//    page with the new key and value, so it does not matter whether the global write has landed;
+//    the block with mt == 0 among them also writes them to the cache (write_kv != 0).
+//  * Each block writes its split's partial result, then takes a ticket from a counter of its
+//    (sequence, kv head, head tile); the block that draws the last ticket merges all splits in
+//    split order (so the result does not depend on which block that is), writes the output and
+//    resets the counter. counters: sequences * nkv * mtiles ints, zero before the first launch.
+__global__ void __launch_bounds__(128)
+attn_decode_fused_kernel(const bf16* qkv, const float* parts, int n_parts, size_t part_stride, const float* __restrict__ qn,
+                         const float* __restrict__ kn, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                         float eps, bf16* out, float* ws_acc, float* ws_ml, int* counters, bf16* k_store, bf16* v_store,
+                         const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
+                         int write_kv) {
+    extern __shared__ __align__(16) bf16 smem[];
+    __shared__ __align__(16) bf16 q_rows[16 * HD];
+    __shared__ __align__(16) bf16 kv_new[2 * HD];
+    __shared__ int last_flag;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int G = nh / nkv, mtiles = (G + 15) / 16;
+    const int split = blockIdx.x, nsplit = gridDim.x;
+    const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
+    const int b = blockIdx.z;
+    const int head0 = kvh * G + mt * 16;
+    const int heads_here = min(16, G - mt * 16);
+    const int pos = row_pos[b];
+    const int* pt = page_table + (size_t)b * pt_stride;
+    const int width = (nh + 2 * nkv) * HD;
+    constexpr int HALF = HD / 2;
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+    if (pos >= 0) {
+        const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+        const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
+        const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
+        const int jt0 = t_lo + split * per, jt1 = min(t_hi + 1, jt0 + per);  // [jt0, jt1)
+        if (jt0 < jt1) {  // the first page is on its way while q and k are being prepared
+            stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
+            cp_async_commit();
+        }
+        // ---- q heads of this block, the new k and v: rows heads_here + 2, one warp per row
+        auto xin = [&](int col) {
+            if (parts == nullptr) return __bfloat162float(qkv[(size_t)b * width + col]);
+            float s = 0.f;
+            for (int k = 0; k < n_parts; k++) s += parts[(size_t)k * part_stride + (size_t)b * width + col];
+            return s;
+        };
+        for (int r = warp; r < heads_here + 2; r += 4) {
+            const bool is_q = r < heads_here, is_k = r == heads_here;
+            const int col0 = is_q ? (head0 + r) * HD : (is_k ? (nh + kvh) * HD : (nh + nkv + kvh) * HD);
+            bf16* dst = is_q ? q_rows + r * HD : kv_new + (is_k ? 0 : HD);
+            if (!is_q && !is_k) {  // value: plain copy
+                for (int d = lane; d < HD; d += 32) dst[d] = __float2bfloat16_rn(xin(col0 + d));
+                continue;
+            }
+            float x1[(HALF + 31) / 32], x2[(HALF + 31) / 32];
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < (HALF + 31) / 32; i++) {
+                const int d = lane + 32 * i;
+                x1[i] = d < HALF ? xin(col0 + d) : 0.f;
+                x2[i] = d < HALF ? xin(col0 + d + HALF) : 0.f;
+                ss += x1[i] * x1[i] + x2[i] * x2[i];
+            }
+            const float* nw = is_q ? qn : kn;
+            float rs = 1.f;
+            if (nw) {
+                ss = warp_sum(ss);
+                rs = rsqrtf(ss / (float)HD + eps);
+            }
+#pragma unroll
+            for (int i = 0; i < (HALF + 31) / 32; i++) {
+                const int d = lane + 32 * i;
+                if (d < HALF) {
+                    float a1 = x1[i] * rs, a2 = x2[i] * rs;
+                    if (nw) a1 *= nw[d], a2 *= nw[d + HALF];
+                    float o1 = a1, o2 = a2;
+                    if (cos_t) {
+                        const float c = cos_t[(size_t)pos * HALF + d], s = sin_t[(size_t)pos * HALF + d];
+                        o1 = a1 * c - a2 * s;
+                        o2 = a2 * c + a1 * s;
+                    }
+                    dst[d] = __float2bfloat16_rn(o1);
+                    dst[d + HALF] = __float2bfloat16_rn(o2);
+                }
+            }
+        }
+        __syncthreads();
+
+        if (jt0 < jt1) {
+            if (write_kv && mt == 0 && jt1 == t_hi + 1) {  // this block owns the new token's page: store k, v
+                const size_t off = kv_offset(pt[t_hi], nkv, kvh, pos % DK_PAGE, HD);
+                for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+                    k_store[off + d] = kv_new[d];
+                    v_store[off + d] = kv_new[HD + d];
+                }
+            }
+            uint32_t qf[HD / 16][4];
+            load_q_frags(qf, g < heads_here ? q_rows + g * HD : nullptr, g + 8 < heads_here ? q_rows + (g + 8) * HD : nullptr);
+            const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
+            for (int jt = jt0; jt < jt1; jt++) {
+                const int cur = (jt - jt0) & 1;
+                if (jt + 1 < jt1) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
+                cp_async_commit();
+                cp_async_wait<1>();
+                __syncthreads();
+                bf16* Ks = smem + cur * STAGE_ELEMS;
+                if (write_kv && jt == t_hi) {  // the new token's row: from this block's own copy
+                    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+                        Ks[(pos % DK_PAGE) * KSTR + d] = kv_new[d];
+                        Ks[TILE_ELEMS + (pos % DK_PAGE) * KSTR + d] = kv_new[HD + d];
+                    }
+                    __syncthreads();
+                }
+                const int key0 = jt * DK_PAGE + warp * 16;
+                if (key0 <= pos && key0 + 15 >= key_lo)
+                    warp_attend<16>(qf, Ks + warp * 16 * KSTR, Ks + TILE_ELEMS + warp * 16 * KSTR, key0, lo, hi, sl2, m, l, acc);
+                __syncthreads();
+            }
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    float* sm_m = reinterpret_cast<float*>(smem);  // [4][16]
+    float* sm_l = sm_m + 64;                       // [4][16]
+    float* sm_a = sm_l + 64;                       // [4][16][HD]
+    __syncthreads();
+    if (t == 0) {
+        sm_m[warp * 16 + g] = m[0];
+        sm_m[warp * 16 + g + 8] = m[1];
+        sm_l[warp * 16 + g] = l[0];
+        sm_l[warp * 16 + g + 8] = l[1];
+    }
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; nt++) {
+        float* a0 = sm_a + ((size_t)(warp * 16 + g) * HD) + nt * 8 + 2 * t;
+        float* a1 = sm_a + ((size_t)(warp * 16 + g + 8) * HD) + nt * 8 + 2 * t;
+        a0[0] = acc[nt][0];
+        a0[1] = acc[nt][1];
+        a1[0] = acc[nt][2];
+        a1[1] = acc[nt][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < heads_here * HD; idx += blockDim.x) {
+        const int row = idx / HD, d = idx % HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + row]);
+        float L = 0.f, A = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float f = exp2f(sm_m[w * 16 + row] - M);
+                L += sm_l[w * 16 + row] * f;
+                A += sm_a[(size_t)(w * 16 + row) * HD + d] * f;
+            }
+        }
+        const size_t head = (size_t)b * nh + head0 + row;
+        if (nsplit == 1) {
+            out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        } else {
+            ws_acc[(head * nsplit + split) * HD + d] = A;
+            if (d == 0) {
+                ws_ml[(head * nsplit + split) * 2] = M;
+                ws_ml[(head * nsplit + split) * 2 + 1] = L;
+            }
+        }
+    }
+    if (nsplit == 1) return;
+    // ---- the last block of this (sequence, kv head, head tile) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* c = counters + ((size_t)b * nkv + kvh) * mtiles + mt;
+        const int ticket = atomicAdd(c, 1);
+        last_flag = ticket == nsplit - 1;
+        if (last_flag) *c = 0;  // everyone has drawn: ready for the next launch
+    }
+    __syncthreads();
+    if (!last_flag) return;
+    __threadfence();
+    for (int idx = threadIdx.x; idx < heads_here * HD; idx += blockDim.x) {
+        const int row = idx / HD, d = idx % HD;
+        const size_t head = (size_t)b * nh + head0 + row;
+        const volatile float* ml = ws_ml + head * nsplit * 2;
+        const volatile float* wa = ws_acc + head * nsplit * HD;
+        float M = -INFINITY;
+        for (int s = 0; s < nsplit; s++) M = fmaxf(M, ml[2 * s]);
+        float L = 0.f, A = 0.f;
+        if (M != -INFINITY) {
+            for (int s = 0; s < nsplit; s++) {
+                const float f = exp2f(ml[2 * s] - M);
+                L += ml[2 * s + 1] * f;
+                A += wa[(size_t)s * HD + d] * f;
+            }
+        }
+        out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+    }
+}
+
+// qkv [n_seq, (nh + 2 nkv) * HD] bf16, or parts != null: n_parts float32 partial sums of it
+// (part_stride elements apart). ws_acc / ws_ml as dk_attn_decode_bf16; counters: n_seq * nkv *
+// ceil(G / 16) ints, zeroed once by the caller (the kernel leaves them zero).
+DK_EXPORT int dk_attn_decode_fused(const void* qkv, const float* parts, int n_parts, long long part_stride, const float* qn,
+                                   const float* kn, const float* cos_t, const float* sin_t, float eps, void* out,
+                                   float* ws_acc, float* ws_ml, int* counters, void* k_store, void* v_store,
+                                   const int* row_pos, const int* page_table, int pt_stride, int n_seq, int nh, int nkv,
+                                   int window, float scale, int nsplit, int write_kv, cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int G = nh / nkv, mtiles = (G + 15) / 16;
+    return dk_launch(attn_decode_fused_kernel, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), SMEM_BYTES, st,
+                     (const bf16*)qkv, parts, n_parts, (size_t)part_stride, qn, kn, cos_t, sin_t, eps, (bf16*)out, ws_acc,
+                     ws_ml, counters, (bf16*)k_store, (bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv, window,
+                     scale * 1.4426950408889634f, write_kv);
+}

@@ -395,3 +395,46 @@ def test_gemv_stream(M, N, K):
     r = api.gemv_stream(x, w, None, api.MODE_STORE, plan)
     close(r.sum() if isinstance(r, api.Partial) else r, ref, torch.bfloat16, "stream planned")
     assert api.stream_plan(M, N, 9728, api.MODE_SILU) is None and api.stream_plan(M, N, 9728, api.MODE_STORE, True)[0] >= 4
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window,nsplit", [(4, 2, 16, 0, 1), (32, 8, 128, 0, 6), (6, 2, 48, 0, 8),
+                                                     (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 32)])
+@pytest.mark.parametrize("as_partial", [False, True])
+def test_attention_decode_fused(nh, nkv, hd, window, nsplit, as_partial):
+    """The one-launch decode mixer (norm + rotation + cache write + attention + merge) against the
+    separate kernels: same outputs, and the cache holds the new keys and values afterwards."""
+    before = [0, 63, 64, 300, 1000, 5]
+    n = len(before)
+    s = paged_setup(before, [1] * n, nkv, hd, torch.bfloat16, seed=60)
+    width = (nh + 2 * nkv) * hd
+    parts = rnd(3, n + 1, width, seed=61, scale=0.6)
+    qkv = parts.sum(0).to(torch.bfloat16)
+    arg = api.Partial(parts) if as_partial else qkv
+    qn, kn = 1 + 0.1 * rnd(hd, seed=62), 1 + 0.1 * rnd(hd, seed=63)
+    cos, sin = plain.rope_tables(1e4, hd, 1100)
+    cos_h, sin_h = cos[:, :hd // 2].contiguous().to(DEV), sin[:, :hd // 2].contiguous().to(DEV)
+    row_pos = torch.cat([s["row_pos"], torch.tensor([-1], dtype=torch.int32, device=DEV)])     # one padding row
+    table = torch.cat([s["table"], -torch.ones(1, s["table"].shape[1], dtype=torch.int32, device=DEV)])
+    row_seq = torch.arange(n + 1, dtype=torch.int32, device=DEV)
+    # reference: the separate kernels on a copy of the cache
+    k_ref, v_ref = s["k_store"].clone(), s["v_store"].clone()
+    q = torch.empty(n + 1, nh * hd, dtype=torch.bfloat16, device=DEV)
+    api.qk_norm_rope_write(qkv if not as_partial else api.Partial(parts), q, qn, kn, cos_h, sin_h, row_pos, row_seq, table,
+                           k_ref, v_ref, nh, nkv, hd, 1e-6)
+    want = torch.empty_like(q)
+    api.attention_generic(q, want, k_ref, v_ref, row_pos, row_seq, table, nh, nkv, hd, window, hd ** -0.5)
+    out = torch.full_like(q, float("nan"))
+    ws = api.attention_decode_ws(n + 1, nh, hd, nsplit, DEV)
+    counters = torch.zeros((n + 1) * nkv * ((nh // nkv + 15) // 16), dtype=torch.int32, device=DEV)
+    for _ in range(2):                                               # twice: the counters must come back to zero
+        api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh,
+                                   nkv, hd, window, hd ** -0.5, nsplit, *ws, counters)
+        close(out[:n], want[:n], torch.bfloat16, "fused decode attention")
+        assert float(out[n:].float().abs().max()) == 0.0 and int(counters.abs().sum()) == 0
+    assert torch.equal(s["k_store"], k_ref) and torch.equal(s["v_store"], v_ref)
+    # a layer that only reads another layer's cache: nothing is written
+    k0 = s["k_store"].clone()
+    api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd,
+                               window, hd ** -0.5, nsplit, *ws, counters, write_kv=False)
+    assert torch.equal(s["k_store"], k0)
+    close(out[:n], want[:n], torch.bfloat16, "fused decode attention, read-only")

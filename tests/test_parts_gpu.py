@@ -145,3 +145,29 @@ def test_block_part(dtype):
     h = h0.to(DEV)
     pending = part.forward(ctx, h, None, cache.views(0))
     close(h + tensor(pending, dtype).float(), ref, dtype, "block")                   # the block leaves its last add to the next norm
+
+
+def test_attention_part_fused_decode_agrees_with_separate_kernels():
+    """The one-launch decode path of the attention part gives what the three-kernel path gives."""
+    H, nh, nkv, hd = 64, 4, 2, 32
+    spec = AttentionSpec(H, nh, nkv, hd, hd ** -0.5, RMSNormSpec(hd, 1e-6), RotaryHalfSpec(hd, 1e4), None)
+    outs = []
+    for fused in (False, True):
+        part = build_part(spec, Runtime(DEV, torch.bfloat16))
+        part.fuse_decode = fused
+        bind(part, {k.split("self_attn.")[1]: v for k, v in mixer_weights(H, nh, nkv, hd, 70).items()}, torch.bfloat16)
+        cache = Cache([part.cache_requests()], 64 * 4, 4, DEV)
+        slots = [cache.begin(), cache.begin()]
+        a = rnd(80 + 3 + 10, H, seed=71).to(DEV, torch.bfloat16)
+        ctx = build_context(cache, [(slots[0], [0] * 80, []), (slots[1], [0] * 3, [])], DEV)
+        part.forward(ctx, cache.views(0), a[:83])
+        cache.commit(slots[0], 80), cache.commit(slots[1], 3)
+        steps = []
+        for i in range(5):
+            ctx = build_context(cache, [(slots[0], [0], []), (slots[1], [0], [])], DEV, pad_to=4)
+            x = torch.zeros(4, H, dtype=torch.bfloat16, device=DEV)
+            x[:2] = a[83 + 2 * i:85 + 2 * i]
+            steps.append(tensor(part.forward(ctx, cache.views(0), x), torch.bfloat16)[:2].float())
+            cache.commit(slots[0], 1), cache.commit(slots[1], 1)
+        outs.append(torch.cat(steps))
+    close(outs[1], outs[0].cpu(), torch.bfloat16, "fused vs separate decode")
