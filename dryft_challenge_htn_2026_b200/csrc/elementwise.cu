@@ -184,6 +184,152 @@ __global__ void gather_rows_f32_kernel(const float* src, const int* rows,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Wide variants for many rows of bfloat16 (prefill): 16-byte accesses instead of 2-byte ones.
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x, f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; i++) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+// silu(gate) * up, 8 outputs a thread; I % 8 == 0.
+__global__ void silu_mul_wide_kernel(const bf16* gu, bf16* out, size_t n8, int I8) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n8) return;
+    const size_t r = idx / I8, c = idx % I8;
+    const uint4* row = reinterpret_cast<const uint4*>(gu) + r * 2 * I8;
+    float g[8], u[8], o[8];
+    unpack8(row[c], g);
+    unpack8(row[I8 + c], u);
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = g[i] / (1.f + expf(-g[i])) * u[i];
+    reinterpret_cast<uint4*>(out)[idx] = pack8(o);
+}
+
+// h += delta; a = rmsnorm(h) * w for bfloat16 delta / a, 8 elements a thread per pass, values kept
+// in registers between the two passes. H % 8 == 0 and H <= 8 * 4 * blockDim.x.
+__global__ void add_rmsnorm_wide_kernel(float* h, const bf16* delta, const float* __restrict__ w, float eps, int H, bf16* a) {
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t row = blockIdx.x;
+    float4* hr = reinterpret_cast<float4*>(h + row * H);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * H) : nullptr;
+    const int n8 = H / 8;
+    float v[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n8) {
+            const float4 x0 = hr[2 * i], x1 = hr[2 * i + 1];
+            v[it][0] = x0.x, v[it][1] = x0.y, v[it][2] = x0.z, v[it][3] = x0.w;
+            v[it][4] = x1.x, v[it][5] = x1.y, v[it][6] = x1.z, v[it][7] = x1.w;
+            if (dr) {
+                float d[8];
+                unpack8(dr[i], d);
+#pragma unroll
+                for (int k = 0; k < 8; k++) v[it][k] += d[k];
+                hr[2 * i] = make_float4(v[it][0], v[it][1], v[it][2], v[it][3]);
+                hr[2 * i + 1] = make_float4(v[it][4], v[it][5], v[it][6], v[it][7]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) ss += v[it][k] * v[it][k];
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    uint4* ar = reinterpret_cast<uint4*>(a + row * H);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int it = 0; it < 4; it++) {
+        const int i = threadIdx.x + it * blockDim.x;
+        if (i < n8) {
+            const float4 w0 = wr[2 * i], w1 = wr[2 * i + 1];
+            float o[8] = {v[it][0] * rs * w0.x, v[it][1] * rs * w0.y, v[it][2] * rs * w0.z, v[it][3] * rs * w0.w,
+                          v[it][4] * rs * w1.x, v[it][5] * rs * w1.y, v[it][6] * rs * w1.z, v[it][7] * rs * w1.w};
+            ar[i] = pack8(o);
+        }
+    }
+}
+
+// q/k norm + rotation + cache write for bfloat16 with head sizes that are multiples of 16: a warp
+// takes one (token, head); lane l holds elements [8l', 8l'+8) of each half of the head.
+// HALF8 = head_dim / 16 lanes are active per half.
+__global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, const float* __restrict__ qn,
+                                               const float* __restrict__ kn, const float* __restrict__ cos_t,
+                                               const float* __restrict__ sin_t, const int* row_pos, const int* row_seq,
+                                               const int* page_table, int pt_stride, bf16* k_store, bf16* v_store,
+                                               int n_tok, int nh, int nkv, int hd, float eps, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int heads = nh + 2 * nkv;
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= (long long)n_tok * heads) return;
+    const int t = (int)(wid / heads), hidx = (int)(wid % heads);
+    const int pos = row_pos[t];
+    if (pos < 0) return;
+    const int half = hd >> 1, half8 = hd >> 4;
+    const bf16* x = qkv + (size_t)t * heads * hd + (size_t)hidx * hd;
+    bf16* dst;
+    if (hidx < nh) {
+        dst = q_out + ((size_t)t * nh + hidx) * hd;
+    } else {
+        if (!write_kv) return;
+        const int kvh = (hidx - nh) % nkv;
+        const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
+        dst = (hidx < nh + nkv ? k_store : v_store) + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+    }
+    if (hidx >= nh + nkv) {  // value head: plain copy, 16 bytes a lane
+        if (lane < 2 * half8) reinterpret_cast<uint4*>(dst)[lane] = reinterpret_cast<const uint4*>(x)[lane];
+        return;
+    }
+    const bool on = lane < half8;
+    float x1[8], x2[8];
+    float ss = 0.f;
+    if (on) {
+        unpack8(reinterpret_cast<const uint4*>(x)[lane], x1);
+        unpack8(reinterpret_cast<const uint4*>(x + half)[lane], x2);
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss += x1[i] * x1[i] + x2[i] * x2[i];
+    }
+    const float* nw = hidx < nh ? qn : kn;
+    float rs = 1.f;
+    if (nw) {
+        ss = warp_sum(ss);
+        rs = rsqrtf(ss / (float)hd + eps);
+    }
+    if (!on) return;
+    float o1[8], o2[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = 8 * lane + i;
+        float a1 = x1[i] * rs, a2 = x2[i] * rs;
+        if (nw) a1 *= nw[d], a2 *= nw[d + half];
+        o1[i] = a1, o2[i] = a2;
+        if (cos_t) {
+            const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
+            o1[i] = a1 * c - a2 * s;
+            o2[i] = a2 * c + a1 * s;
+        }
+    }
+    reinterpret_cast<uint4*>(dst)[lane] = pack8(o1);
+    reinterpret_cast<uint4*>(dst + half)[lane] = pack8(o2);
+}
+
+// ---------------------------------------------------------------------------------------------
 #define DISPATCH_T(dtype, ...)                         \
     if ((dtype) == 0) { typedef float T; __VA_ARGS__; } \
     else { typedef bf16 T; __VA_ARGS__; }
@@ -199,6 +345,9 @@ DK_EXPORT int dk_embed_rmsnorm(int dtype, const int* tok, const void* embed, con
 DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float* parts, int n_parts,
                              long long part_stride, const int* rows, const float* w, float eps, int n_rows, int H,
                              void* a, cudaStream_t st) {
+    if (dtype == 1 && parts == nullptr && rows == nullptr && H % 8 == 0 && H <= 8 * 4 * row_threads(H) && n_rows > 64)
+        return dk_launch(add_rmsnorm_wide_kernel, dim3(n_rows), dim3(row_threads(H)), 0, st, h, (const bf16*)delta, w, eps,
+                         H, (bf16*)a);
     size_t smem = rows ? (size_t)H * sizeof(float) : 0;
     if (smem > 48 * 1024) {
         DISPATCH_T(dtype, cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -210,6 +359,9 @@ DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float
 
 DK_EXPORT int dk_silu_mul(int dtype, const void* gu, void* out, long long n_rows, int I, cudaStream_t st) {
     size_t n = (size_t)n_rows * I;
+    if (dtype == 1 && I % 8 == 0)
+        return dk_launch(silu_mul_wide_kernel, dim3((unsigned)((n / 8 + 255) / 256)), dim3(256), 0, st, (const bf16*)gu,
+                         (bf16*)out, n / 8, I / 8);
     DISPATCH_T(dtype, return dk_launch(silu_mul_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st,
                                        (const T*)gu, (T*)out, n, I));
 }
@@ -222,6 +374,10 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* par
     if (hd % 2 != 0 || hd > 256) return (int)cudaErrorInvalidValue;
     long long warps = (long long)n_tok * (nh + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
+    if (dtype == 1 && parts == nullptr && hd % 16 == 0 && n_tok > 64)
+        return dk_launch(qk_norm_rope_write_wide_kernel, dim3(blocks), dim3(128), 0, st, (const bf16*)qkv, (bf16*)q_out, qn,
+                         kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride, (bf16*)k_store, (bf16*)v_store, n_tok,
+                         nh, nkv, hd, eps, write_kv);
     DISPATCH_T(dtype, return dk_launch(qk_norm_rope_write_kernel<T>, dim3(blocks), dim3(128), 0, st, (const T*)qkv,
                                        parts, n_parts, (size_t)part_stride, (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
                                        (T*)k_store, (T*)v_store, n_tok, nh, nkv, hd, eps, write_kv));
