@@ -423,3 +423,42 @@ def attention_decode_fused(qkv, out, q_norm_w, k_norm_w, cos, sin, eps, k_store,
                                          _p(v_store), _p(row_pos), _p(page_table), page_table.shape[1], n_seq, n_heads,
                                          n_kv_heads, int(window or 0), c_float(scale), nsplit, int(bool(write_kv)),
                                          _stream()), "attention_decode_fused")
+
+
+# ------------------------------------------------------------- tensor-core product for many rows
+_tc_err = None
+
+
+def gemm_tc(x, w, mode=MODE_STORE, out=None):
+    """out = x . w^T (mode MODE_STORE) or silu(x . gate^T) * (x . up^T) (mode MODE_SILU, w = [gate;
+    up]) on tcgen05 tensor cores, TMA-fed, float32 accumulation in tensor memory, bfloat16 out."""
+    global _tc_err
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
+    if K % 8 or w.shape[1] != K or mode not in (MODE_STORE, MODE_SILU):
+        raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} mode {mode} not supported (K % 8 == 0)")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    if _tc_err is None:
+        _tc_err = torch.zeros(1, dtype=torch.int32, device=x.device)
+    lib = _lib("gemm_tc.cu")
+    _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(out), M, N, K, mode, _p(_tc_err), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_fills_gpu(M, N, min_fill=0.8):
+    """Whether gemm_tc's 128 x 256 output tiles, one persistent block per SM, keep the last wave
+    at least ``min_fill`` full on average; below that the library's smaller tiles win."""
+    tiles = ((M + 127) // 128) * ((N + 255) // 256)
+    waves = tiles / SM_COUNT
+    return waves / -(-tiles // SM_COUNT) >= min_fill
+
+
+def gemm_tc_check():
+    """Raises if a bounded wait inside gemm_tc ran out since the last check (synchronises)."""
+    if _tc_err is not None:
+        code = int(_tc_err.item())
+        if code:
+            _tc_err.zero_()
+            raise KernelError(f"gemm_tc: a bounded wait ran out (code {code}); its results are not valid")

@@ -101,7 +101,8 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
     """Compiles every kernel file (attention once per head size), in parallel."""
     from concurrent.futures import ThreadPoolExecutor
 
-    jobs = [("elementwise.cu", None), ("attention_generic.cu", None), ("gemm.cu", None), ("sampling.cu", None),
+    jobs = [("elementwise.cu", None), ("attention_generic.cu", None), ("gemm.cu", None), ("gemv_stream.cu", None),
+            ("gemm_tc.cu", None), ("sampling.cu", None),
             ("sample_noalloc.cu", None)]
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:

@@ -264,9 +264,10 @@ __global__ void add_rmsnorm_wide_kernel(float* h, const bf16* delta, const float
     }
 }
 
-// q/k norm + rotation + cache write for bfloat16 with head sizes that are multiples of 16: a warp
-// takes one (token, head); lane l holds elements [8l', 8l'+8) of each half of the head.
-// HALF8 = head_dim / 16 lanes are active per half.
+// q/k norm + rotation + cache write for bfloat16 with head sizes that are multiples of 16. A group
+// of GS lanes (GS = the power of two >= head_dim / 16) takes one (token, head); a warp takes 32 / GS
+// of them. Lane j of a group holds elements [8j, 8j+8) of each half of the head.
+template <int GS>
 __global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, const float* __restrict__ qn,
                                                const float* __restrict__ kn, const float* __restrict__ cos_t,
                                                const float* __restrict__ sin_t, const int* row_pos, const int* row_seq,
@@ -274,48 +275,49 @@ __global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, con
                                                int n_tok, int nh, int nkv, int hd, float eps, int write_kv) {
     pdl_wait();
     pdl_launch_dependents();
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, j = lane % GS;
     const int heads = nh + 2 * nkv;
-    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= (long long)n_tok * heads) return;
-    const int t = (int)(wid / heads), hidx = (int)(wid % heads);
-    const int pos = row_pos[t];
-    if (pos < 0) return;
+    const long long item = ((long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * (32 / GS) + lane / GS;
+    const bool live = item < (long long)n_tok * heads;
+    const int t = live ? (int)(item / heads) : 0, hidx = live ? (int)(item % heads) : 0;
+    const int pos = live ? row_pos[t] : -1;
     const int half = hd >> 1, half8 = hd >> 4;
+    const bool is_v = hidx >= nh + nkv;
+    const bool work = pos >= 0 && (hidx < nh || write_kv);
     const bf16* x = qkv + (size_t)t * heads * hd + (size_t)hidx * hd;
-    bf16* dst;
-    if (hidx < nh) {
-        dst = q_out + ((size_t)t * nh + hidx) * hd;
-    } else {
-        if (!write_kv) return;
-        const int kvh = (hidx - nh) % nkv;
-        const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
-        dst = (hidx < nh + nkv ? k_store : v_store) + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+    bf16* dst = nullptr;
+    if (work) {
+        if (hidx < nh) {
+            dst = q_out + ((size_t)t * nh + hidx) * hd;
+        } else {
+            const int kvh = (hidx - nh) % nkv;
+            const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
+            dst = (hidx < nh + nkv ? k_store : v_store) + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+        }
     }
-    if (hidx >= nh + nkv) {  // value head: plain copy, 16 bytes a lane
-        if (lane < 2 * half8) reinterpret_cast<uint4*>(dst)[lane] = reinterpret_cast<const uint4*>(x)[lane];
-        return;
-    }
-    const bool on = lane < half8;
+    const bool on = work && j < half8;
     float x1[8], x2[8];
     float ss = 0.f;
     if (on) {
-        unpack8(reinterpret_cast<const uint4*>(x)[lane], x1);
-        unpack8(reinterpret_cast<const uint4*>(x + half)[lane], x2);
+        const uint4 r1 = reinterpret_cast<const uint4*>(x)[j], r2 = reinterpret_cast<const uint4*>(x + half)[j];
+        if (is_v) {  // value head: plain copy
+            reinterpret_cast<uint4*>(dst)[j] = r1;
+            reinterpret_cast<uint4*>(dst + half)[j] = r2;
+        }
+        unpack8(r1, x1);
+        unpack8(r2, x2);
 #pragma unroll
         for (int i = 0; i < 8; i++) ss += x1[i] * x1[i] + x2[i] * x2[i];
     }
+#pragma unroll
+    for (int o = GS / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // within the group of GS lanes
+    if (!on || is_v) return;
     const float* nw = hidx < nh ? qn : kn;
-    float rs = 1.f;
-    if (nw) {
-        ss = warp_sum(ss);
-        rs = rsqrtf(ss / (float)hd + eps);
-    }
-    if (!on) return;
+    const float rs = nw ? rsqrtf(ss / (float)hd + eps) : 1.f;
     float o1[8], o2[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const int d = 8 * lane + i;
+        const int d = 8 * j + i;
         float a1 = x1[i] * rs, a2 = x2[i] * rs;
         if (nw) a1 *= nw[d], a2 *= nw[d + half];
         o1[i] = a1, o2[i] = a2;
@@ -325,8 +327,8 @@ __global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, con
             o2[i] = a2 * c + a1 * s;
         }
     }
-    reinterpret_cast<uint4*>(dst)[lane] = pack8(o1);
-    reinterpret_cast<uint4*>(dst + half)[lane] = pack8(o2);
+    reinterpret_cast<uint4*>(dst)[j] = pack8(o1);
+    reinterpret_cast<uint4*>(dst + half)[j] = pack8(o2);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -374,10 +376,21 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* par
     if (hd % 2 != 0 || hd > 256) return (int)cudaErrorInvalidValue;
     long long warps = (long long)n_tok * (nh + 2 * nkv);
     unsigned blocks = (unsigned)((warps + 3) / 4);
-    if (dtype == 1 && parts == nullptr && hd % 16 == 0 && n_tok > 64)
-        return dk_launch(qk_norm_rope_write_wide_kernel, dim3(blocks), dim3(128), 0, st, (const bf16*)qkv, (bf16*)q_out, qn,
-                         kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride, (bf16*)k_store, (bf16*)v_store, n_tok,
-                         nh, nkv, hd, eps, write_kv);
+    if (dtype == 1 && parts == nullptr && hd % 16 == 0 && n_tok > 64) {
+        const int half8 = hd / 16;
+        const int gs = half8 <= 1 ? 1 : half8 <= 2 ? 2 : half8 <= 4 ? 4 : half8 <= 8 ? 8 : 16;
+        const unsigned wblocks = (unsigned)((warps + 4LL * (32 / gs) - 1) / (4LL * (32 / gs)));
+#define ROPE_WIDE(GS)                                                                                                  \
+    return dk_launch(qk_norm_rope_write_wide_kernel<GS>, dim3(wblocks), dim3(128), 0, st, (const bf16*)qkv, (bf16*)q_out, \
+                     qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride, (bf16*)k_store, (bf16*)v_store, n_tok, \
+                     nh, nkv, hd, eps, write_kv)
+        if (gs == 1) ROPE_WIDE(1);
+        if (gs == 2) ROPE_WIDE(2);
+        if (gs == 4) ROPE_WIDE(4);
+        if (gs == 8) ROPE_WIDE(8);
+        ROPE_WIDE(16);
+#undef ROPE_WIDE
+    }
     DISPATCH_T(dtype, return dk_launch(qk_norm_rope_write_kernel<T>, dim3(blocks), dim3(128), 0, st, (const T*)qkv,
                                        parts, n_parts, (size_t)part_stride, (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
                                        (T*)k_store, (T*)v_store, n_tok, nh, nkv, hd, eps, write_kv));

@@ -1,0 +1,307 @@
+// The prefill matrix product on the 5th-generation tensor cores:
+//   out[M,N] = x[M,K] . W[N,K]^T                         (mode 0, bfloat16 out)
+//   out[M,N] = silu(x . Wgate^T) * (x . Wup^T)           (mode 2, W = [gate; up], N rows each)
+// float32 accumulation in tensor memory. Reference: the reference engine hands these products to
+// the library (engine/fused.py:993-995) and runs SiLU*up as a separate kernel (:175-188); here the
+// gated product writes silu(gate)*up directly, so the [M, 2N] intermediate never exists.
+//
+// One persistent block per SM walks 128 x BN tiles of the output (mode 2: 128 rows x 128 outputs,
+// from a gate tile and an up tile side by side in one 256-column accumulator); two accumulators
+// alternate in tensor memory so the epilogue of a tile overlaps the mma of the next.
+//   warp 0   producer: one thread issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte
+//            swizzle) of x [128 x 64] and W [BN x 64] into a 4-stage shared-memory ring; an
+//            mbarrier per stage counts the bytes.
+//   warp 1   allocates BN columns of tensor memory; one thread issues tcgen05.mma
+//            (cta_group::1, kind::f16, M = 128, N = BN, K = 16, four per stage) from shared-memory
+//            matrix descriptors, and tcgen05.commit hands each stage back / signals the epilogue.
+//   warps 2-5 epilogue: tcgen05.ld of the accumulator (32 lanes x 32 columns a warp at a time),
+//            conversion, SiLU*up in mode 2, bfloat16 stores.
+// Rows of x beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA; stores are
+// masked. K must be a multiple of 8 (16-byte global strides). Every mbarrier wait is bounded: if
+// one runs out the block stores a code in *err, still frees its tensor memory, and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int SPIN_LIMIT = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (int i = 0; i < SPIN_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+                     smem_u32(dst)),
+                 "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
+// groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// MODE 0: W tile rows [n0, n0+BN). MODE 2 (BN = 256): rows [n0, n0+128) of gate at accumulator
+// columns 0..127 and the same rows of up (row offset N) at columns 128..255; n0 counts outputs.
+// Persistent: block b computes tiles b, b + gridDim.x, ... (row tiles fastest, so the blocks that
+// run together share a panel of W). Two accumulators of BN columns alternate in tensor memory: the
+// mma of a tile runs while the epilogue warps drain the tile before it.
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, bf16* out, int M,
+               int N, int K, int m_tiles, int tiles, int* err) {
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;   // outputs per tile
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // the swizzle pattern repeats every 1024 bytes
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;     // [2] mma -> epilogue
+    uint64_t* acc_empty = acc_full + 2;      // [2] epilogue -> mma
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (K + BK - 1) / BK;
+
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);     // one arrival per epilogue warp
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {  // ------------------------------------------------------------ producer
+            int it = 0;   // stages issued so far, over all tiles of this block
+            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+                        atomicExch(err, 1);
+                        tile = tiles;
+                        break;
+                    }
+                    uint8_t* stage = smem + s * STAGE_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
+                    if (MODE == 2) {
+                        tma_load_2d(stage + A_BYTES, &map_w, kb * BK, n0, &full[s]);
+                        tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
+                    } else {
+                        tma_load_2d(stage + A_BYTES, &map_w, kb * BK, n0, &full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // ---------------------------------------------------------- mma issuer
+            int it = 0, iter = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, iter++) {
+                const int buf = iter & 1;
+                if (iter >= 2 && !mbar_wait(&acc_empty[buf], ((iter >> 1) & 1) ^ 1)) {   // the epilogue has drained it
+                    atomicExch(err, 4);
+                    ok = false;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem + buf * BN;
+                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+                        atomicExch(err, 2);
+                        ok = false;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)
+                        umma_f16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb | k) != 0);
+                    umma_commit(&empty[s]);   // the stage is free once these mma have read it
+                }
+                umma_commit(&acc_full[buf]);  // arrives when every mma above has finished
+            }
+        }
+    } else {  // -------------------------------------------------------------------------- epilogue
+        const int q = warp & 3;               // the quarter of the tensor-memory lanes this warp may read
+        int iter = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, iter++) {
+            const int buf = iter & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
+            const int row = m0 + q * 32 + lane;
+            if (!mbar_wait(&acc_full[buf], (iter >> 1) & 1)) {
+                atomicExch(err, 3);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = tmem + buf * BN + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < OUT_COLS; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(acc + c, v);
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) f[i] = __uint_as_float(v[i]);
+                if (MODE == 2) {
+                    uint32_t u[32];
+                    tmem_ld32(acc + OUT_COLS + c, u);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+                }
+                if (row < M) {
+                    bf16* dst = out + (size_t)row * N + n0 + c;
+                    if (n0 + c + 32 <= N && (N % 8 == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 pk;
+                            __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) p[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
+                            *reinterpret_cast<uint4*>(dst + i) = pk;
+                        }
+                    } else {
+                        for (int i = 0; i < 32; i++)
+                            if (n0 + c + i < N) dst[i] = __float2bfloat16_rn(f[i]);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[buf])) : "memory");
+            }
+        }
+    }
+    // ---- teardown: everyone arrives, then the allocating warp frees the tensor memory
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    pdl_launch_dependents();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, cols]: tiles of box_rows x 64 columns, 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int BN, int MODE>
+int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, cudaStream_t st) {
+    constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;
+    constexpr size_t smem = 1024 + (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    CUtensorMap mx, mw;
+    int e = make_map(&mx, x, M, K, BM);
+    if (e) return e;
+    e = make_map(&mw, W, MODE == 2 ? 2LL * N : N, K, MODE == 2 ? BN / 2 : BN);
+    if (e) return e;
+    const int m_tiles = (M + BM - 1) / BM, tiles = m_tiles * ((N + OUT_COLS - 1) / OUT_COLS);
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(tiles < sms ? tiles : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
+                     m_tiles, tiles, err);
+}
+
+}  // namespace
+
+// x [M,K] bf16, W [N,K] bf16 (mode 2: [2N,K] = gate rows then up rows), out [M,N] bf16.
+// err: device int, receives a code if a bounded wait ran out. K % 8 == 0; 16-byte aligned x, W.
+DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, cudaStream_t st) {
+    if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
+    if (mode == 2) return launch<256, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, st);
+    if (mode == 0) return launch<256, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, st);
+    return (int)cudaErrorInvalidValue;
+}

@@ -13,6 +13,7 @@ from collections import deque
 import numpy as np
 import torch
 
+from ..csrc import api
 from ..csrc.api import PAGE
 from ..sampling import Sampler, seed_words
 from .batch import StepContext
@@ -245,6 +246,7 @@ class GpuBackend:
         logits = r.model.forward(ctx, r.cache)
         for s, p in zip(slots, prompts):
             r.cache.commit(s, len(p))
+        api.gemm_tc_check()
         st = self.state
         st.fill(self.seqs)
         n = len(prompts)

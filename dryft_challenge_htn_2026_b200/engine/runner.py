@@ -8,6 +8,7 @@ padded to a common length, and a sequence's result does not depend on the others
 import torch
 
 from ..cache import Cache
+from ..csrc import api
 from .batch import build_context
 
 
@@ -50,4 +51,6 @@ class Runner:
         logits = self.model.forward(ctx, self.cache)
         for slot, tokens, _ in entries:
             self.cache.commit(slot, len(tokens))
+        if not ctx.is_decode:
+            api.gemm_tc_check()
         return logits

@@ -1,8 +1,10 @@
 """out = x . W^T for a weight [out, in] without bias: picks the kernel by dtype and row count.
 
-float32: the CUDA-core sgemm for every size (a true 32-bit product). bfloat16: the skinny
-tensor-core kernel that streams the weights once for up to 64 rows (decode), the library matrix
-product for more rows (prefill; the reference uses the library there too, engine/fused.py:993-995)."""
+float32: the CUDA-core sgemm for every size (a true 32-bit product). bfloat16: the streaming
+kernels that read the weights once for up to 64 rows (decode); for more rows (prefill) the
+TMA + tcgen05 kernel, always for the gated product (SiLU*up fused into its epilogue) and otherwise
+when its 128 x 256 tiles fill the GPU's waves, else the library matrix product (the reference uses
+the library for all of these, engine/fused.py:993-995)."""
 import torch
 
 from ..csrc import api
@@ -38,6 +40,8 @@ def _linear(x, w, mode, allow_partial):
         return api.gemv_bf16(x, w, None, mode, api.gemv_plan(M, N, K, mode, allow_partial))
     if mode == STORE_F32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
+    if K % 8 == 0 and (mode == SILU or api.gemm_tc_fills_gpu(M, N)):
+        return api.gemm_tc(x, w, mode)          # TMA + tcgen05, SiLU*up fused into the epilogue
     y = torch.mm(x, w.t())
     if mode == SILU:
         out = torch.empty((M, N), dtype=x.dtype, device=x.device)

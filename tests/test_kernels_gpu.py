@@ -438,3 +438,17 @@ def test_attention_decode_fused(nh, nkv, hd, window, nsplit, as_partial):
                                window, hd ** -0.5, nsplit, *ws, counters, write_kv=False)
     assert torch.equal(s["k_store"], k0)
     close(out[:n], want[:n], torch.bfloat16, "fused decode attention, read-only")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (100, 300, 72), (300, 200, 136), (1000, 520, 2560), (65, 2560, 1024)])
+def test_gemm_tc(M, N, K):
+    """The TMA + tcgen05 product against x.w^T in float32: full tiles, ragged edges in M, N and K,
+    several tiles per block (persistent loop, both accumulators), plain and SiLU*up epilogues."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=81), rnd(2 * N, K, dtype=torch.bfloat16, seed=82, scale=0.05)
+    ref = x.float() @ w.float().T
+    close(api.gemm_tc(x, w[:N].contiguous()), ref[:, :N], torch.bfloat16, "gemm_tc")
+    g, u = ref[:, :N], ref[:, N:]
+    close(api.gemm_tc(x, w, api.MODE_SILU), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gemm_tc silu")
+    api.gemm_tc_check()
+    with pytest.raises(api.KernelError):
+        api.gemm_tc(rnd(70, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16))
