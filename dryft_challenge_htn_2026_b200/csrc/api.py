@@ -462,3 +462,27 @@ def gemm_tc_check():
         if code:
             _tc_err.zero_()
             raise KernelError(f"gemm_tc: a bounded wait ran out (code {code}); its results are not valid")
+
+
+# --------------------------------------------------------------- tensor-core prefill attention
+TC_ATTENTION_HEAD_DIMS = (64, 128)
+TC_TILE_ROWS = 128
+
+
+def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads, n_kv_heads, head_dim, window,
+                         scale):
+    """Ragged causal attention of query chunks on tcgen05 tensor cores (head sizes 64 and 128).
+    Arguments as ``attention_prefill_bf16`` except that ``tiles`` lists 128-row tiles."""
+    global _tc_err
+    _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2), _need(tiles, "tiles", torch.int32, 2)
+    _need(cu_q, "cu_q", torch.int32, 1), _need(seq_pos0, "seq_pos0", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16, 4)
+    if head_dim not in TC_ATTENTION_HEAD_DIMS or n_heads % n_kv_heads:
+        raise KernelError(f"attention_prefill_tc: head size {head_dim} (64 or 128) / heads {n_heads}:{n_kv_heads} not supported")
+    if _tc_err is None:
+        _tc_err = torch.zeros(1, dtype=torch.int32, device=q.device)
+    lib = _lib("attention_tc.cu", {"HD": head_dim})
+    _check(lib, lib.dk_attn_prefill_tc(_p(q), _p(out), _p(k_store), _p(v_store), c_longlong(q.shape[0]),
+                                       c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
+                                       _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
+                                       c_float(scale), _p(_tc_err), _stream()), "attention_prefill_tc")

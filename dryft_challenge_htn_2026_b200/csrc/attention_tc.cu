@@ -1,0 +1,431 @@
+// Prefill attention on the 5th-generation tensor cores: ragged causal grouped-query flash
+// attention over the paged cache with S = Q.K^T and O += P.V as tcgen05.mma, accumulators in
+// tensor memory, tiles fed by TMA. Built per head size with -DHD=64 or -DHD=128.
+// Formulas as attention_bf16.cu (reference: engine/fused.py:301-343): scores scaled by
+// scale*log2(e), running maximum and sum in float32, P rounded to bfloat16 before P.V.
+//
+// A block owns 128 consecutive queries of one sequence and one query head and walks the keys in
+// blocks of 128 (two cache pages).
+//   warp 9, one thread: TMA loads (Q once; K and V of each block as [64 keys x 64 columns] boxes,
+//       128-byte swizzle, straight from the page the table names).
+//   warp 8, one thread: all tcgen05.mma:
+//       S[128 x 128] = Q.K^T  (both operands from shared memory),
+//       O[128 x HD] += P.V    (P from tensor memory, V from shared memory, N-major).
+//   warps 0-7: softmax, two threads per query row (64 key columns each): they read their part of
+//       the row of S from tensor memory (tcgen05.ld) into registers, agree on the running maximum
+//       through shared memory, rescale their half of the row of O in tensor memory when the
+//       maximum moved, write P as bfloat16 back into tensor memory over S (tcgen05.st), and at the
+//       end normalise and store their half of the row of O.
+// K of the next block is fetched as soon as S has been computed, V as soon as P.V has: the loads
+// overlap the softmax and the other product. Two blocks fit on an SM (96 KB shared, 256 columns of
+// tensor memory each), so one block's softmax overlaps the other's mma.
+// Every mbarrier wait is bounded; a wait that runs out stores a code in *err, and the block still
+// frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#ifndef HD
+#error "compile with -DHD=64 or -DHD=128"
+#endif
+static_assert(HD == 64 || HD == 128, "tensor-core prefill attention is built for head sizes 64 and 128");
+
+#ifdef ATTN_TRACE
+__device__ long long g_trace[512];
+#define TRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && i < 6) g_trace[(slot) + 16 * i] = clock64(); } while (0)
+DK_EXPORT int dk_attn_trace(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)); }
+#else
+#define TRACE(slot)
+#endif
+
+namespace {
+
+constexpr int BM = 128, BN = 128;                 // queries per block, keys per step
+constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms across the head
+constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;
+constexpr int ATOM_ROWS_BYTES = 128 * 128;        // 128 rows of one 64-column atom
+constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
+constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > WAIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+// K-major operand, 128-byte swizzle: rows 128 bytes apart, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// N-major operand (V: keys are the rows in shared memory, the head columns are contiguous),
+// 128-byte swizzle: the next 64 columns are ATOM_ROWS_BYTES away, the next 8 keys 1024 bytes.
+__device__ __forceinline__ uint64_t desc_n_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(ATOM_ROWS_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d),
+                 "l"(a), "l"(b), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }" ::"r"(d),
+                 "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// (no wait inside: call tmem_wait_ld() before the registers are used)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+                     taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                 "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
+// 2^x, one MUFU instruction (-inf gives 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// grid (tiles, nh), 320 threads. tiles[2i] = sequence, tiles[2i+1] = first query (of 128) within
+// the sequence's chunk. q / out [T, nh*HD]; map_q over q as [T, nh*HD]; map_k / map_v over one
+// layer's K / V store as [pages * nkv * 64, HD].
+// Threads 0..255: softmax, two threads per query row (thread t and t+128 share row t & 127 and
+// take 64 of the 128 key columns each; warp w may read the tensor-memory lanes 32 (w % 4)..+31).
+// Warp 8, one thread: every tcgen05.mma. Warp 9, one thread: every TMA load.
+__global__ void __launch_bounds__(320, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, bf16* out, const int* tiles, const int* cu_q,
+                       const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
+                       int* err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
+    const uint32_t q_s = smem_u32(smem), k_s = q_s + Q_BYTES, v_s = k_s + KV_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + 2 * KV_BYTES);
+    uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3, *bar_p = bars + 4, *bar_o = bars + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    float* xch = reinterpret_cast<float*>(bars + 8);        // [2][256] row maxima / sums exchanged between the two threads of a row
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    pdl_wait();
+    const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
+    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
+    const int rows_here = min(BM, q_len - q0);
+    const int flat0 = cu_q[seq] + q0;                      // first flat row of this tile
+    const int* pt = page_table + (size_t)seq * pt_stride;
+    const int max_pos = pos0 + q0 + rows_here - 1, min_pos = pos0 + q0;
+    const int blk_hi = max_pos / BN;
+    const int blk_lo = window > 0 ? max(0, min_pos - window + 1) / BN : 0;
+    const int n_blk = blk_hi - blk_lo + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(bar_q, 1), mbar_init(bar_k, 1), mbar_init(bar_v, 1), mbar_init(bar_s, 1), mbar_init(bar_o, 1);
+        mbar_init(bar_p, 256);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_s = tmem, t_o = tmem + 128;           // S (and P over it) at columns 0..127, O at 128..128+HD
+
+    if (warp == 9) {
+        if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
+            auto load_kv = [&](const CUtensorMap* map, uint32_t dst, int blk, uint64_t* bar) {
+                mbar_expect_tx(bar, KV_BYTES);
+                for (int pg = 0; pg < 2; pg++) {
+                    int page = pt[min(2 * blk + pg, pt_stride - 1)];
+                    if (page < 0) page = 0;                 // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
+                    const int row = (page * nkv + kvh) * DK_PAGE;
+                    for (int hh = 0; hh < HALVES; hh++)
+                        tma_load_2d(dst + hh * ATOM_ROWS_BYTES + pg * (DK_PAGE * 128), map, hh * 64, row, bar);
+                }
+            };
+            mbar_expect_tx(bar_q, Q_BYTES);
+            for (int hh = 0; hh < HALVES; hh++) tma_load_2d(q_s + hh * ATOM_ROWS_BYTES, &map_q, h * HD + hh * 64, flat0, bar_q);
+            load_kv(&map_k, k_s, blk_lo, bar_k);
+            load_kv(&map_v, v_s, blk_lo, bar_v);
+            for (int i = 0; i + 1 < n_blk; i++) {
+                if (!mbar_wait(bar_s, i & 1)) { atomicExch(err, 3); break; }   // S(i) is done with K
+                load_kv(&map_k, k_s, blk_lo + i + 1, bar_k);
+                if (!mbar_wait(bar_o, i & 1)) { atomicExch(err, 3); break; }   // P.V(i) is done with V
+                load_kv(&map_v, v_s, blk_lo + i + 1, bar_v);
+            }
+        }
+    } else if (warp == 8) {
+        if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
+            bool ok = mbar_wait(bar_q, 0);
+            for (int i = 0; i < n_blk && ok; i++) {
+                const uint32_t ph = i & 1;
+                TRACE(0);
+                if (!mbar_wait(bar_k, ph)) { ok = false; break; }
+                TRACE(1);
+                if (i > 0 && !mbar_wait(bar_o, (i - 1) & 1)) { ok = false; break; }   // P (over S) has been consumed by P.V
+                fence_after();
+#pragma unroll
+                for (int hh = 0; hh < HALVES; hh++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        umma_ss(t_s, desc_k_major(q_s + hh * ATOM_ROWS_BYTES + k * 32), desc_k_major(k_s + hh * ATOM_ROWS_BYTES + k * 32),
+                                IDESC_S, (hh | k) != 0);
+                umma_commit(bar_s);
+                TRACE(2);
+                if (!mbar_wait(bar_p, ph)) { ok = false; break; }
+                TRACE(4);
+                if (!mbar_wait(bar_v, ph)) { ok = false; break; }   // P is written, V is here
+                TRACE(5);
+                fence_after();
+#pragma unroll
+                for (int k = 0; k < BN / 16; k++)
+                    umma_ts(t_o, t_s + k * 8, desc_n_major(v_s + k * 16 * 128), IDESC_PV, (i | k) != 0);
+                umma_commit(bar_o);
+                TRACE(6);
+            }
+            if (!ok) atomicExch(err, 1);
+        }
+    } else {  // ------------------------------------------------------------------ softmax, two threads a row
+        const int r = threadIdx.x & 127, half = threadIdx.x >> 7;   // row within the tile = tensor-memory lane; column half
+        const bool valid = r < rows_here;
+        const int qpos = pos0 + q0 + r;
+        const int key_lo = window > 0 ? max(0, qpos - window + 1) : 0;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        const int col0 = half * 64;                          // this thread's key columns within a block
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int i = 0; i < n_blk && ok; i++) {
+            const uint32_t ph = i & 1;
+            const int key0 = (blk_lo + i) * BN + col0;
+            if (threadIdx.x == 0) TRACE(8);
+            if (!mbar_wait(bar_s, ph)) { ok = false; break; }
+            if (threadIdx.x == 0) TRACE(9);
+            fence_after();
+            uint32_t v[2][32];
+            tmem_ld32(t_s + lane_off + col0, v[0]);
+            tmem_ld32(t_s + lane_off + col0 + 32, v[1]);
+            tmem_wait_ld();
+            if (threadIdx.x == 0) TRACE(10);
+            // every key of the block visible to every row of the tile: no per-element test
+            const bool open = window <= 0 && (blk_lo + i) * BN + BN - 1 <= min_pos;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (open) {
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[c][j]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; c++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int key = key0 + c * 32 + j;
+                        const float sc = (valid && key <= qpos && key >= key_lo) ? __uint_as_float(v[c][j]) : -INFINITY;
+                        v[c][j] = __float_as_uint(sc);
+                        mx4[j & 3] = fmaxf(mx4[j & 3], sc);
+                    }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // sl2 > 0: scaling keeps the order
+            // the row's maximum is over both threads of the row
+            xch[(i & 1) * 256 + threadIdx.x] = mx;
+            if (threadIdx.x == 0) TRACE(7);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (threadIdx.x == 0) TRACE(3);
+            float m_new = fmaxf(m, fmaxf(mx, xch[(i & 1) * 256 + (threadIdx.x ^ 128)]));
+            // a maximum that moved by less than 8 (a factor 256) keeps the old reference: P stays well inside
+            // float32 / bfloat16 range, the final O / l is the same, and O need not be rescaled
+            if (m != -INFINITY && m_new - m < 8.f) m_new = m;
+            const float ms = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = ex2(m - ms);
+            // O of the earlier blocks is rescaled when the reference moved (P.V of the last block must be complete);
+            // each thread of a row takes half of the columns of O
+            if (i > 0) {
+                if (!mbar_wait(bar_o, (i - 1) & 1)) { ok = false; break; }
+                fence_after();
+                if (__any_sync(0xffffffffu, alpha != 1.f)) {   // tcgen05.ld/st are warp-wide: all lanes or none
+#pragma unroll 1
+                    for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(t_o + lane_off + c, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                        tmem_st32(t_o + lane_off + c, o);
+                    }
+                }
+            }
+            if (threadIdx.x == 0) TRACE(11);
+            // P = exp2(S * sl2 - m), its sum, and P as bfloat16 over the columns of S
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t p[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const float e0 = ex2(fmaf(__uint_as_float(v[c][j]), sl2, -ms)), e1 = ex2(fmaf(__uint_as_float(v[c][j + 1]), sl2, -ms));
+                    sum4[(j >> 1) & 3] += e0 + e1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+                    p[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                tmem_st16(t_s + lane_off + (col0 + c * 32) / 2, p);
+            }
+            l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            m = m_new;
+            if (threadIdx.x == 0) TRACE(12);
+            tmem_wait_st();
+            fence_before();
+            mbar_arrive(bar_p);
+            if (threadIdx.x == 0) TRACE(13);
+        }
+        if (ok && n_blk > 0) ok = mbar_wait(bar_o, (n_blk - 1) & 1);
+        // the row's sum is over both threads of the row
+        xch[threadIdx.x] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l += xch[threadIdx.x ^ 128];
+        if (ok) {
+            fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = out + ((size_t)(flat0 + r) * nh + h) * HD;
+#pragma unroll 1
+            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                uint32_t o[32];
+                tmem_ld32(t_o + lane_off + c, o);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 pk;
+                        __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+                        for (int u = 0; u < 4; u++)
+                            pp[u] = __floats2bfloat162_rn(__uint_as_float(o[j + 2 * u]) * inv, __uint_as_float(o[j + 2 * u + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + j) = pk;
+                    }
+                }
+            }
+        } else if (lane == 0) {
+            atomicExch(err, 2);
+        }
+    }
+    fence_before();
+    __syncthreads();
+    pdl_launch_dependents();
+    if (warp == 8) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// Row-major bf16 matrix [rows, cols]: boxes of box_rows x 64 columns, 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+    EncodeTiled enc = encoder();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+DK_EXPORT int dk_attn_tc_head_dim() { return HD; }
+
+// q, out [n_tok, nh*HD] bf16; k_store, v_store [n_pages, nkv, 64, HD] bf16; tiles [n_tiles][2] =
+// (sequence, first query of a 128-row tile within its chunk); err: device int for a wait that ran out.
+DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, const void* v_store, long long n_tok,
+                                 long long n_pages, const int* tiles, int n_tiles, const int* cu_q, const int* seq_pos0,
+                                 const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
+                                 cudaStream_t st) {
+    if (nh % nkv != 0 || err == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
+    constexpr size_t smem = 1024 + Q_BYTES + 2 * KV_BYTES + 8 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr = true;
+    }
+    CUtensorMap mq, mk, mv;
+    int e = make_map(&mq, q, n_tok, (long long)nh * HD, BM);
+    if (!e) e = make_map(&mk, k_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
+    if (!e) e = make_map(&mv, v_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
+    if (e) return e;
+    return dk_launch(attn_prefill_tc_kernel, dim3(n_tiles, nh), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, cu_q,
+                     seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err);
+}

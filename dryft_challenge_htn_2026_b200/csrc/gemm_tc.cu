@@ -27,7 +27,7 @@ namespace {
 
 constexpr int BM = 128, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int SPIN_LIMIT = 1 << 22;
+constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -37,7 +37,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (int i = 0; i < SPIN_LIMIT; i++) {
+    const long long t0 = clock64();
+    for (;;) {
         uint32_t ok;
         asm volatile(
             "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
@@ -45,8 +46,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
             : "r"(smem_u32(bar)), "r"(parity)
             : "memory");
         if (ok) return true;
+        if (clock64() - t0 > WAIT_CYCLES) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(

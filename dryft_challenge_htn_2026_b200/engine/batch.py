@@ -9,7 +9,8 @@ import torch
 
 from ..csrc.api import PAGE
 
-TILE_ROWS = 64  # query rows per block of the prefill attention kernel
+TILE_ROWS = 64        # query rows per block of the mma.sync prefill attention kernel
+WIDE_TILE_ROWS = 128  # query rows per block of the tcgen05 prefill attention kernel
 
 
 class StepContext:
@@ -26,6 +27,7 @@ class StepContext:
     seq_pos0 [n_seq]         tokens the sequence had cached before this step
     want_rows [n_want]       rows whose logits are returned, in request order
     tiles [n_tiles, 2]       (sequence, first query) of each 64-row attention tile, heaviest first
+    tiles_wide [n, 2]        the same for 128-row tiles
     tables[g] [n_seq, P_g]   page ids of each sequence in cache group g
     host                     dict of the same arrays as numpy, for parts that plan on the host
     """
@@ -92,6 +94,12 @@ def build_context(cache, entries, device, scratch_store=None, pad_to=None):
             tiles.append((int(pos0[i]) + min(q0 + TILE_ROWS, int(lens[i])), i, q0))
     tiles.sort(key=lambda t: -t[0])
     tiles = np.array([(t[1], t[2]) for t in tiles], dtype=np.int32).reshape(-1, 2)
+    wide = []
+    for i in range(n_seq):
+        for q0 in range(0, int(lens[i]), WIDE_TILE_ROWS):
+            wide.append((int(pos0[i]) + min(q0 + WIDE_TILE_ROWS, int(lens[i])), i, q0))
+    wide.sort(key=lambda t: -t[0])
+    wide = np.array([(t[1], t[2]) for t in wide], dtype=np.int32).reshape(-1, 2)
     slots = [e[0] for e in entries]
     tables = []
     for g in range(len(cache.groups)):
@@ -100,13 +108,14 @@ def build_context(cache, entries, device, scratch_store=None, pad_to=None):
             t = np.concatenate([t, -np.ones((rows - n_seq, t.shape[1]), np.int32)])
         tables.append(t)
     i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)
-    arrays = [i32(tok), i32(row_seq), i32(row_pos), i32(cu), i32(slots), i32(pos0), i32(want), tiles] + tables
+    arrays = [i32(tok), i32(row_seq), i32(row_pos), i32(cu), i32(slots), i32(pos0), i32(want), tiles, wide] + tables
     dev = _pack(arrays, device)
     ctx = StepContext(scratch_store)
     ctx.n_tok, ctx.n_seq, ctx.n_want, ctx.is_decode = rows, n_seq, len(want), is_decode
     ctx.max_position = int((pos0 + lens).max()) - 1
-    (ctx.tok, ctx.row_seq, ctx.row_pos, ctx.cu_q, ctx.seq_slot, ctx.seq_pos0, ctx.want_rows, ctx.tiles) = dev[:8]
-    ctx.tables = dev[8:]
+    (ctx.tok, ctx.row_seq, ctx.row_pos, ctx.cu_q, ctx.seq_slot, ctx.seq_pos0, ctx.want_rows, ctx.tiles,
+     ctx.tiles_wide) = dev[:9]
+    ctx.tables = dev[9:]
     ctx.host = dict(lens=lens, pos0=pos0, cu_q=cu, slots=slots, row_seq=row_seq, row_pos=row_pos)
     if is_decode:
         ctx.n_seq = rows  # the decode kernels run one sequence per row, padding rows included

@@ -136,7 +136,7 @@ class DecodeState:
         ctx.tok, ctx.row_seq, ctx.row_pos, ctx.seq_slot = d["tok"], d["row_seq"], d["row_pos"], d["seq_slot"]
         ctx.want_rows = torch.arange(rows, dtype=torch.int32, device=dev)
         ctx.tables = [cut(self.dev, 6 + g, (rows, width)) for g in range(ng)]
-        ctx.cu_q = ctx.seq_pos0 = ctx.tiles = None
+        ctx.cu_q = ctx.seq_pos0 = ctx.tiles = ctx.tiles_wide = None
         ctx.host = None
         self.ctx = ctx
         self.temps = d["temps"].view(torch.float32)

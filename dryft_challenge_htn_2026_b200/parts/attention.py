@@ -107,6 +107,9 @@ class GQAAttention(Part):
                                         lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, a.device))
             api.attention_decode_bf16(q, o, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window, s.scale, nsplit,
                                       ws_acc, ws_ml)
+        elif hd in api.TC_ATTENTION_HEAD_DIMS:   # tcgen05: S and P.V in tensor memory, TMA-fed
+            api.attention_prefill_tc(q, o, kv.k, kv.v, ctx.tiles_wide, ctx.cu_q, ctx.seq_pos0, table, nh, nkv, hd,
+                                     window, s.scale)
         else:
             api.attention_prefill_bf16(q, o, kv.k, kv.v, ctx.tiles, ctx.cu_q, ctx.seq_pos0, table, nh, nkv, hd,
                                        window, s.scale)

@@ -23,6 +23,10 @@ TINY = {
     "C": dict(vocab_size=300, hidden_size=72, intermediate_size=104, num_hidden_layers=4, num_attention_heads=3,
               num_key_value_heads=1, head_dim=48, rms_norm_eps=3e-6, rope_theta=500000.0, tie_word_embeddings=True,
               max_position_embeddings=512, use_sliding_window=True, sliding_window=37, max_window_layers=2),
+    # head size 64: the size the tcgen05 attention kernel is built for besides 128
+    "D": dict(vocab_size=320, hidden_size=128, intermediate_size=192, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=100000.0, tie_word_embeddings=False,
+              max_position_embeddings=512),
 }
 
 

@@ -129,6 +129,7 @@ def test_build_context_rows_positions_and_tiles():
     assert ctx.row_seq[4:6].tolist() == [0, 1] and ctx.seq_pos0.tolist() == [0, 0, 0]
     assert sorted(map(tuple, ctx.tiles.tolist())) == [(0, 0), (1, 0), (1, 64), (1, 128), (2, 0)]
     assert tuple(ctx.tiles[0].tolist()) == (1, 128)              # the tile that sees most keys goes first
+    assert sorted(map(tuple, ctx.tiles_wide.tolist())) == [(0, 0), (1, 0), (1, 128), (2, 0)]
     assert ctx.tables[0].shape == (3, 3) and ctx.tables[0][0].tolist()[1:] == [-1, -1]
     for s, n in ((a, 5), (b, 130), (c, 1)):
         cache.commit(s, n)

@@ -452,3 +452,21 @@ def test_gemm_tc(M, N, K):
     api.gemm_tc_check()
     with pytest.raises(api.KernelError):
         api.gemm_tc(rnd(70, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("nh,nkv,hd,window,before,new", [
+    (2, 1, 128, 0, [0], [128]), (8, 2, 128, 0, [0, 100, 0, 64, 130], [70, 150, 1, 64, 5]), (4, 4, 64, 0, [0, 100], [200, 129]),
+    (3, 1, 64, 90, [0, 100], [200, 129]), (6, 2, 128, 40, [300, 0], [140, 400])])
+def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
+    """The tcgen05 prefill attention against the float32 reference: ragged chunks on top of cached
+    tokens, several key blocks per tile (rescaling of O), group sizes 1..4, a window, padding rows."""
+    s = paged_setup(before, new, nkv, hd, torch.bfloat16, seed=90)
+    q = rnd(s["n_tok"], nh * hd, dtype=torch.bfloat16, seed=91)
+    tiles = sorted(((before[i] + min(q0 + 128, new[i]), i, q0) for i in range(len(new)) for q0 in range(0, new[i], 128)),
+                   reverse=True)
+    tiles = torch.tensor([(t[1], t[2]) for t in tiles], dtype=torch.int32, device=DEV).reshape(-1, 2)
+    out = torch.full_like(q, float("nan"))
+    api.attention_prefill_tc(q, out, s["k_store"], s["v_store"], tiles, s["cu_q"], s["pos0"], s["table"], nh, nkv, hd, window,
+                             hd ** -0.5)
+    api.gemm_tc_check()
+    close(out, ref_attention(q, s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_prefill_tc")

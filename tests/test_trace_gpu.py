@@ -11,7 +11,8 @@ from helpers import TINY, make_folder, random_tokens, run_trace, tolerance
 pytestmark = pytest.mark.gpu
 
 # request lengths per configuration: a single token, a page boundary (64, 65), several pages
-LENGTHS = {"A": [40, 33, 64, 100, 65, 37], "B": [33, 64, 47, 130, 38, 90], "C": [35, 129, 64, 80, 200, 41]}
+LENGTHS = {"A": [40, 33, 64, 100, 65, 37], "B": [33, 64, 47, 130, 38, 90], "C": [35, 129, 64, 80, 200, 41],
+           "D": [300, 34, 129, 64, 260, 161]}
 TAIL = 32
 
 
@@ -48,7 +49,7 @@ def build_steps(seqs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_matches_plain_however_the_tokens_are_cut(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name, seed=5)
     cfg, t = plain.read_model(folder)
