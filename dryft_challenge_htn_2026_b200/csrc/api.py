@@ -227,9 +227,11 @@ def attention_decode_ws(n_seq, n_heads, head_dim, nsplit, device):
 
 
 def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads, head_dim, window, scale,
-                          nsplit, ws_acc=None, ws_ml=None):
+                          nsplit, ws_acc=None, ws_ml=None, merge_in_kernel=False):
     """One query token per sequence over its cached keys [.., row_pos] (tensor cores, keys split
-    over ``nsplit`` blocks and merged)."""
+    over ``nsplit`` blocks and merged by a second kernel, or with ``merge_in_kernel`` by the last
+    block of each head group in the same launch: 1.5 to 5 us slower on B200, the tickets cost more
+    than the dependent launch)."""
     _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
     n_seq = q.shape[0]
@@ -239,10 +241,14 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
                 or ws_ml.numel() < n_seq * n_heads * nsplit * 2:
             raise KernelError("attention_decode_bf16: scratch too small for this batch and split count")
     lib = _attn_lib(head_dim)
+    counters = None
+    if 1 < nsplit <= 32 and merge_in_kernel:
+        group = n_heads // max(1, n_kv_heads)
+        counters = tile_counters(q.device, n_seq * n_kv_heads * ((group + 15) // 16))
     _check(lib, lib.dk_attn_decode_bf16(_p(q), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos),
                                         _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
-                                        int(window or 0), c_float(scale), nsplit, _stream()), "attention_decode_bf16",
-           2 if nsplit > 1 else 1)
+                                        int(window or 0), c_float(scale), nsplit, _p(counters), _stream()),
+           "attention_decode_bf16", 2 if nsplit > 1 and counters is None else 1)
 
 
 # ---------------------------------------------------------------------------------------- products
@@ -363,35 +369,97 @@ def stream_plan(M, N, K, mode, allow_partial=False):
     return sk, blocks
 
 
-def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
+class Added:
+    """The result of a product that has already been added into the float32 residual stream
+    ``h`` in place. ``sq`` [ceil(width / 16), 16] float32 holds, per 16 columns, the sums of
+    squares of the new h's rows (row j in column j): what an RMSNorm of h needs."""
+
+    def __init__(self, h, sq):
+        self.h, self.sq = h, sq
+
+
+class Normed:
+    """rmsnorm(h) * weight that has not been computed yet: a product that can (``gemv_stream``)
+    makes it from ``h`` and the sums of squares while it loads its input; anything else calls
+    ``tensor()``. It stands for h as it is now: use it before the next product is added into h."""
+
+    def __init__(self, h, sq, weight, eps, dtype):
+        self.h, self.sq, self.weight, self.eps, self.dtype = h, sq, weight, eps, dtype
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def tensor(self):
+        out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
+        add_rmsnorm(self.h, None, self.weight, self.eps, out)
+        return out
+
+
+_counters = {}
+
+
+def tile_counters(device, n):
+    """Zeroed int32 counters that kernels with an in-kernel meeting point (split-K slices of a
+    tile, key splits of a head) draw tickets from; every such kernel leaves them zero."""
+    if n > (1 << 16):
+        raise KernelError(f"{n} meeting points in one launch are more than the counters hold")
+    key = (device.type, device.index)
+    if key not in _counters:
+        _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
+    return _counters[key]
+
+
+def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None):
     """The weight-streaming skinny product (asynchronous copies into shared-memory rings,
     tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Same results and
-    return convention as ``gemv_bf16``."""
-    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
+    return convention as ``gemv_bf16``. ``x`` may be a ``Normed`` (the norm is applied while x is
+    loaded; modes STORE and SILU). With ``residual`` (float32 [M, N], mode STORE) the product is
+    added into it in place and an ``Added`` is returned."""
+    lazy = isinstance(x, Normed)
+    if lazy:
+        if x.dtype != torch.bfloat16 or mode == MODE_STORE_F32 or residual is not None:
+            raise KernelError("gemv_stream: a deferred norm goes with bfloat16, modes STORE and SILU, and no residual")
+        _need(x.h, "h", torch.float32, 2), _need(x.sq, "sq", torch.float32, 2), _need(x.weight, "norm_w", torch.float32, 1)
+    else:
+        _need(x, "x", torch.bfloat16, 2)
+    _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2), _need(residual, "residual", torch.float32, 2)
     M, K = x.shape
     N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
     if M > STREAM_MAX_ROWS or K % 16:
         raise KernelError(f"gemv_stream: {M} rows (max {STREAM_MAX_ROWS}) / inner size {K} (multiple of 16) not supported")
     if w.shape[1] != K:
         raise KernelError(f"gemv_stream: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
-    sk, blocks = plan or stream_plan(M, N, K, mode) or (0, 0)
+    if lazy and (x.sq.shape[0] != (K + 15) // 16 or x.sq.shape[1] != 16 or x.weight.numel() != K):
+        raise KernelError("gemv_stream: the deferred norm's sums of squares or weight do not fit the input width")
+    if residual is not None and (mode != MODE_STORE or tuple(residual.shape) != (M, N)):
+        raise KernelError("gemv_stream: a residual goes with mode STORE and has the output's shape")
+    sk, blocks = plan or stream_plan(M, N, K, mode, residual is not None) or (0, 0)
     if sk < 1 or blocks < sk or ((K + sk - 1) // sk + 15) // 16 * 16 > 2560:
         raise KernelError(f"gemv_stream: K = {K} in {sk} slices on {blocks} blocks is not supported "
                           "(a slice holds at most 2560 elements, and there is a block per slice at least)")
-    ws = None
+    ws = sq = counters = None
     if sk > 1:
         if mode == MODE_SILU:
             raise KernelError("gemv_stream: the SiLU epilogue cannot be split over K")
-        ws = torch.empty((sk, M, N), dtype=torch.float32, device=x.device)
-    else:
+        ws = torch.empty((sk, M, N), dtype=torch.float32, device=w.device)
+    if residual is not None:
+        sq = torch.empty(((N + 15) // 16, 16), dtype=torch.float32, device=w.device)
+        counters = tile_counters(w.device, (N + 15) // 16)
+    elif sk == 1:
         want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
         if out is None:
-            out = torch.empty((M, N), dtype=want, device=x.device)
+            out = torch.empty((M, N), dtype=want, device=w.device)
         elif out.dtype != want or tuple(out.shape) != (M, N):
             raise KernelError(f"gemv_stream: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
     lib = _lib("gemv_stream.cu", STREAM_BUILD)
-    _check(lib, lib.dk_gemv_stream(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, _stream()),
-           "gemv_stream")
+    fuse = 1 if lazy else 2 if residual is not None else 0
+    _check(lib, lib.dk_gemv_stream(None if lazy else _p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, fuse,
+                                   _p(x.h) if lazy else None, _p(x.sq) if lazy else None, x.sq.shape[0] if lazy else 0,
+                                   _p(x.weight) if lazy else None, c_float(x.eps if lazy else 0.0), _p(residual), _p(sq),
+                                   _p(counters), _stream()), "gemv_stream")
+    if residual is not None:
+        return Added(residual, sq)
     return Partial(ws) if sk > 1 else out
 
 

@@ -235,8 +235,10 @@ attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v
 // ws_acc [(b*nh + head)*nsplit + split][HD] and ws_ml [...][2] = (max in log2 domain, row sum).
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
-                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2) {
+                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
+                   int* counters) {
     extern __shared__ __align__(16) bf16 smem[];
+    __shared__ int is_last;
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -334,6 +336,49 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
             }
         }
     }
+    if (nsplit == 1 || counters == nullptr) return;
+    // the block that draws the last ticket of this (sequence, kv head, head tile) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* c = counters + ((size_t)b * nkv + kvh) * mtiles + mt;
+        const int ticket = atomicAdd(c, 1);
+        is_last = ticket == nsplit - 1;
+        if (is_last) *c = 0;  // everyone has drawn: ready for the next launch
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // one warp per head; lane s holds split s's (max, sum) (nsplit <= 32 here), and the loads of
+    // the partial outputs do not depend on one another, so they are all in flight together
+    for (int row = warp; row < heads_here; row += 4) {
+        const size_t head = (size_t)b * nh + head0 + row;
+        const float* ml = ws_ml + head * nsplit * 2;
+        const float* wa = ws_acc + head * nsplit * HD;
+        const float Ms = lane < nsplit ? __ldcg(ml + 2 * lane) : -INFINITY;
+        const float Ls = lane < nsplit ? __ldcg(ml + 2 * lane + 1) : 0.f;
+        float M = Ms;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+        const float fs = M == -INFINITY ? 0.f : exp2f(Ms - M);   // this split's weight
+        float L = Ls * fs;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int base = 0; base < HD; base += 64) {
+            const int d0 = base + lane * 2;
+            const bool ok = d0 < HD;
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+            for (int s = 0; s < nsplit; s++) {
+                const float f = __shfl_sync(0xffffffffu, fs, s);
+                const float2 v = ok ? __ldcg(reinterpret_cast<const float2*>(wa + (size_t)s * HD + d0)) : make_float2(0.f, 0.f);
+                a0 += v.x * f;
+                a1 += v.y * f;
+            }
+            if (ok) *reinterpret_cast<uint32_t*>(out + head * HD + d0) = pack_bf16(a0 * inv, a1 * inv);
+        }
+    }
 }
 
 // grid (sequences * nh), HD threads or fewer looping: merges the splits of one head.
@@ -380,18 +425,21 @@ DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store
                      window, scale * 1.4426950408889634f);
 }
 
-// ws_acc: n_seq*nh*nsplit*HD floats, ws_ml: n_seq*nh*nsplit*2 floats (unused when nsplit == 1)
+// ws_acc: n_seq*nh*nsplit*HD floats, ws_ml: n_seq*nh*nsplit*2 floats (unused when nsplit == 1).
+// counters: null (a second kernel merges the splits) or n_seq * nkv * ceil(G / 16) zeroed ints (the
+// last block of each head group merges them in the same launch and leaves the counters zero).
 DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float* ws_ml, const void* k_store,
                                   const void* v_store, const int* row_pos, const int* page_table, int pt_stride,
-                                  int n_seq, int nh, int nkv, int window, float scale, int nsplit, cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1) return (int)cudaErrorInvalidValue;
+                                  int n_seq, int nh, int nkv, int window, float scale, int nsplit, int* counters,
+                                  cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1 || (counters != nullptr && nsplit > 32)) return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
     e = dk_launch(attn_decode_kernel, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), SMEM_BYTES, st, (const bf16*)q,
                   (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
-                  nh, nkv, window, scale * 1.4426950408889634f);
-    if (e || nsplit == 1) return e;
+                  nh, nkv, window, scale * 1.4426950408889634f, counters);
+    if (e || nsplit == 1 || counters != nullptr) return e;   // (callers give counters only for nsplit <= 32)
     return dk_launch(attn_combine_kernel, dim3(n_seq * nh), dim3(HD < 128 ? HD : 128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, nsplit);
 }

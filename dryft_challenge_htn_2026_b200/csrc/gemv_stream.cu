@@ -20,6 +20,16 @@
 // the engine's request rate; register streaming in the mma fragment layout, which touches 128
 // bytes of 16 rows at a time, stayed near 4.9 TB/s; re-fetching x with every stage cost half as
 // much SM ingress again as the weights.)
+//
+// Two fusions with the residual stream of a pre-norm block, so that a decode step needs no
+// separate add+norm launch between its products:
+//  * FUSE 2 (the producer): the product is added into the float32 residual stream h_out [M,N] in
+//    place. With SK > 1 the slices of a tile meet through a counter: every block stores its
+//    partial sums, the block that draws the last ticket adds the slices up in slice order (so the
+//    result does not depend on which block that is) and owns the tile's piece of h_out. It also
+//    stores the tile's contribution to every row's sum of squares of the new h, sq_out[tile][16].
+//  * FUSE 1 (the consumer): x is not given; the block makes it from the residual stream,
+//    x = h_in * rsqrt(sum(sq_in) / K + eps) * norm_w in bfloat16, while it fills shared memory.
 // Requires K % 16 == 0, 16-byte aligned x and W, a slice of at most XMAX elements.
 #include "common.cuh"
 
@@ -59,13 +69,26 @@ __device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
 // Slice length for SK slices of K: a multiple of 16.
 __host__ __device__ __forceinline__ int slice_len(int K, int SK) { return ((K + SK - 1) / SK + 15) / 16 * 16; }
 
+struct Fuse {
+    const float* h_in;    // FUSE 1: residual stream [M,K]
+    const float* sq_in;   //         [sq_tiles][16] sums of squares of its rows, one line per 16 columns
+    const float* norm_w;  //         [K]
+    float eps;
+    int sq_tiles;
+    float* h_out;         // FUSE 2: residual stream [M,N], += product
+    float* sq_out;        //         [tiles][16]
+    int* counters;        //         [tiles], zero before and after every launch
+};
+
 // MR: rows of x kept (8 or 16, M <= MR). MODE as in gemm.cu. Mode 2: a tile's rows 0-7 are the
 // gate rows of 8 outputs and rows 8-15 their up rows, so a tile covers 8 outputs.
 // gridDim.x is a multiple of SK: block b has slice b % SK and tiles b / SK, + gridDim.x / SK, ...
-template <int MR, int MODE>
+template <int MR, int MODE, int FUSE>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK,
-                   int tiles) {
+                   int tiles, Fuse fu) {
+    __shared__ float rstd_s[16];
+    __shared__ int last_flag;
     constexpr int OUTS = MODE == 2 ? 8 : 16;  // outputs per tile
     constexpr int NT = MR / 8;                // 8-wide batch tiles
     extern __shared__ __align__(128) uint8_t smem[];
@@ -108,7 +131,49 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
     pdl_wait();
     if (tid == 0) pdl_launch_dependents();
     // x rows of this block's slice, once
-    {
+    if (FUSE == 1) {
+        constexpr int U = 20;                 // float4 loads in flight per thread
+        const int row_quads = klen / 4;       // 4 floats in, 8 bytes out
+        const int total = M * row_quads;
+        float4 hv[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) {         // the first batch goes out before the sums of squares are awaited
+            const int c = tid + u * WARPS * 32;
+            if (c < total) hv[u] = __ldcg(reinterpret_cast<const float4*>(fu.h_in + (size_t)(c / row_quads) * K + k_begin + (c % row_quads) * 4));
+        }
+        for (int j = warp; j < M; j += WARPS) {
+            float ss = 0.f;
+#pragma unroll 8
+            for (int i = lane; i < fu.sq_tiles; i += 32) ss += __ldcg(fu.sq_in + i * 16 + j);
+            ss = warp_sum(ss);
+            if (lane == 0) rstd_s[j] = rsqrtf(ss / (float)K + fu.eps);
+        }
+        __syncthreads();
+        for (int base = 0; base < total; base += U * WARPS * 32) {
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int c = base + tid + u * WARPS * 32;
+                if (c < total) {
+                    const int m = c / row_quads, j = c % row_quads;
+                    const float4 wv = *reinterpret_cast<const float4*>(fu.norm_w + k_begin + j * 4);
+                    const float rs = rstd_s[m];
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(hv[u].x * rs * wv.x, hv[u].y * rs * wv.y);
+                    __nv_bfloat162 hi = __floats2bfloat162_rn(hv[u].z * rs * wv.z, hv[u].w * rs * wv.w);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(xs + m * x_stride + j * 8) = pk;
+                }
+            }
+            const int next = base + U * WARPS * 32;
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int c = next + tid + u * WARPS * 32;
+                if (c < total) hv[u] = __ldcg(reinterpret_cast<const float4*>(fu.h_in + (size_t)(c / row_quads) * K + k_begin + (c % row_quads) * 4));
+            }
+        }
+        __syncthreads();
+    } else {
         const int row_chunks = klen / 8;      // 16-byte chunks per row
         for (int c = tid; c < M * row_chunks; c += WARPS * 32) {
             const int m = c / row_chunks, j = c % row_chunks;
@@ -172,6 +237,54 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
             for (int c = 0; c < 4; c++) acc[0][nt][c] = acc[1][nt][c] = 0.f;
         }
         __syncthreads();
+        if (FUSE == 2) {
+            bool fix = true;
+            if (SK > 1) {
+                for (int o = tid; o < OUTS * MR; o += WARPS * 32) {
+                    const int i = o % OUTS, j = o / OUTS;
+                    const int n = tile * OUTS + i;
+                    if (n < N && j < M) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int w = 0; w < WARPS; w++) v += red[w * (WR * MR) + i * MR + j];
+                        ws[((size_t)slice * M + j) * N + n] = v;
+                    }
+                }
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) {
+                    const int ticket = atomicAdd(fu.counters + tile, 1);
+                    last_flag = ticket == SK - 1;
+                    if (last_flag) fu.counters[tile] = 0;   // every slice has drawn: ready for the next launch
+                }
+                __syncthreads();
+                fix = last_flag != 0;
+                if (fix) __threadfence();
+            }
+            if (fix) {
+                for (int o = tid; o < OUTS * MR; o += WARPS * 32) {   // all threads: the shuffles below need whole warps
+                    const int i = o % OUTS, j = o / OUTS;
+                    const int n = tile * OUTS + i;
+                    float sq = 0.f;
+                    if (n < N && j < M) {
+                        float v = 0.f;
+                        if (SK > 1) {
+#pragma unroll 8
+                            for (int sl = 0; sl < SK; sl++) v += __ldcg(ws + ((size_t)sl * M + j) * N + n);
+                        } else {
+#pragma unroll
+                            for (int w = 0; w < WARPS; w++) v += red[w * (WR * MR) + i * MR + j];
+                        }
+                        const float hv = fu.h_out[(size_t)j * N + n] + v;
+                        fu.h_out[(size_t)j * N + n] = hv;
+                        sq = hv * hv;
+                    }
+#pragma unroll
+                    for (int d = 8; d >= 1; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);   // over the tile's 16 columns
+                    if (i == 0 && j < M) fu.sq_out[(size_t)tile * 16 + j] = sq;
+                }
+            }
+        } else
         for (int o = tid; o < OUTS * MR; o += WARPS * 32) {
             const int i = o % OUTS, j = o / OUTS;
             const int n = tile * OUTS + i;
@@ -195,21 +308,23 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
     cp_async_wait<0>();
 }
 
-template <int MR, int MODE>
-int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int blocks, cudaStream_t st) {
+template <int MR, int MODE, int FUSE>
+int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int blocks, const Fuse& fu,
+           cudaStream_t st) {
     const size_t smem = (size_t)WARPS * DEPTH * STAGE_BYTES + (size_t)WARPS * WR * MR * sizeof(float) +
                         (size_t)MR * (slice_len(K, SK) * 2 + 16);
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<MR, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<MR, MODE, FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
         if (e != cudaSuccess) return (int)e;
         attr_smem = smem;
     }
     const int tiles = MODE == 2 ? (N + 7) / 8 : (N + 15) / 16;
     blocks = blocks / SK * SK;
     if (blocks > tiles * SK) blocks = tiles * SK;
-    return dk_launch(gemv_stream_kernel<MR, MODE>, dim3(blocks), dim3(WARPS * 32), smem, st, x, W, out, ws, M, N, K, SK,
-                     tiles);
+    return dk_launch(gemv_stream_kernel<MR, MODE, FUSE>, dim3(blocks), dim3(WARPS * 32), smem, st, x, W, out, ws, M, N, K,
+                     SK, tiles, fu);
 }
 
 }  // namespace
@@ -217,17 +332,30 @@ int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int
 // x [M,K] bf16 (M <= 16), W [N,K] bf16 (mode 2: [2N,K]); SK slices of K (SK > 1: float32 partial
 // sums ws [SK][M][N], modes 0 and 1); `blocks` persistent blocks, at least SK, rounded down to a
 // multiple of SK. A slice, ceil(K / SK) rounded up to 16, may have at most 2560 elements.
+// fuse 1 (modes 0 and 2, K % 4 == 0): x == null, made from h_in [M,K] float32, the per-tile sums of
+// squares sq_in [sq_tiles][16] of its rows, norm_w [K] and eps. fuse 2 (mode 0): the product is
+// added into h_out [M,N] float32, sq_out [ceil(N/16)][16] gets the new rows' sums of squares per
+// 16 columns; counters: ceil(N/16) ints, zero (the kernel leaves them zero); ws needed if SK > 1.
 DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
-                             int blocks, cudaStream_t st) {
+                             int blocks, int fuse, const float* h_in, const float* sq_in, int sq_tiles, const float* norm_w,
+                             float eps, float* h_out, float* sq_out, int* counters, cudaStream_t st) {
     if (M < 1 || M > 16 || K % 16 != 0 || SK < 1 || blocks < SK || slice_len(K, SK) > XMAX) return (int)cudaErrorInvalidValue;
     if (SK > 1 && (mode == 2 || ws == nullptr)) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
+    if (fuse == 1 && (mode == 1 || !h_in || !sq_in || !norm_w || ((uintptr_t)h_in | (uintptr_t)norm_w) % 16 != 0))
+        return (int)cudaErrorInvalidValue;
+    if (fuse == 2 && (mode != 0 || !h_out || !sq_out || (SK > 1 && !counters))) return (int)cudaErrorInvalidValue;
+    if (fuse == 0 && !x) return (int)cudaErrorInvalidValue;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-#define GS_CASE(MR)                                                                        \
-    if (mode == 0) return launch<MR, 0>(xp, wp, out, ws, M, N, K, SK, blocks, st);         \
-    if (mode == 1) return launch<MR, 1>(xp, wp, out, ws, M, N, K, SK, blocks, st);         \
-    return launch<MR, 2>(xp, wp, out, ws, M, N, K, SK, blocks, st);
+    Fuse fu{h_in, sq_in, norm_w, eps, sq_tiles, h_out, sq_out, counters};
+#define GS_CASE(MR)                                                                                      \
+    if (fuse == 1 && mode == 0) return launch<MR, 0, 1>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);   \
+    if (fuse == 1) return launch<MR, 2, 1>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);                \
+    if (fuse == 2) return launch<MR, 0, 2>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);                \
+    if (mode == 0) return launch<MR, 0, 0>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);                \
+    if (mode == 1) return launch<MR, 1, 0>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);                \
+    return launch<MR, 2, 0>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);
     if (M <= 8) { GS_CASE(8) }
     GS_CASE(16)
 #undef GS_CASE

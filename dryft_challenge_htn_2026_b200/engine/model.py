@@ -7,6 +7,7 @@ import torch
 from ..csrc import api
 from ..parts import ParamDecl, Runtime, build_part
 from ..parts.linear import STORE_F32, linear
+from ..parts.norm import RMSNorm
 
 
 class CausalLM:
@@ -108,6 +109,8 @@ class CausalLM:
             if ctx.n_want == 0:
                 return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
             an = torch.empty((ctx.n_want, s.hidden_size), dtype=rt.dtype, device=rt.device)
+            if isinstance(pending, api.Added) and not isinstance(self.final_norm, RMSNorm):
+                pending = None                      # already in h; only RMSNorm knows the marker
             self.final_norm.add_forward(h, pending, an, rows=ctx.want_rows)
             return linear(an, self.head, STORE_F32)
         finally:

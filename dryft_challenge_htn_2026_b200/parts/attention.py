@@ -15,6 +15,10 @@ from .linear import linear
 
 
 class GQAAttention(Part):
+    # forward takes residual= and a deferred norm (see parts.block); measured slower than the separate
+    # add+norm kernel on B200 (the small kernel hides behind the next product's weight prefetch), so off
+    fuses_residual = False
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         s = spec
@@ -66,8 +70,9 @@ class GQAAttention(Part):
         if self.position is not None and getattr(self.position, "fused_tables", False):
             self.position.tables(max_positions)
 
-    def forward(self, ctx, views, a, writes=True):
+    def forward(self, ctx, views, a, writes=True, residual=None):
         s, kv = self.spec, views[0]
+        dtype, dev = self.rt.dtype, self.rt.device
         nh, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
         table = ctx.tables[kv.group]
         qkv = linear(a, self.w_qkv, ctx=ctx, allow_partial=True)
@@ -78,33 +83,33 @@ class GQAAttention(Part):
                 cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
             else:
                 if isinstance(qkv, api.Partial):
-                    qkv = qkv.sum(a.dtype)
+                    qkv = qkv.sum(dtype)
                 self.position.apply(qkv, ctx, nh, nkv, hd)
         qn = self.q_norm.weight if self.q_norm else None
         kn = self.k_norm.weight if self.k_norm else None
         eps = s.qk_norm.eps if s.qk_norm else 0.0
         window = s.window or 0
-        o = torch.empty((ctx.n_tok, nh * hd), dtype=a.dtype, device=a.device)
-        if a.dtype == torch.bfloat16 and ctx.is_decode and self.fuse_decode:
+        o = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
+        if dtype == torch.bfloat16 and ctx.is_decode and self.fuse_decode:
             # one kernel: q/k norm + rotation, cache write, attention over the cache, merge of the splits
             nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
             ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
-                                        lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, a.device))
+                                        lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, dev))
             counters = ctx.scratch(("attn_counters", ctx.n_seq, nkv, nh),
                                    lambda: torch.zeros(ctx.n_seq * nkv * ((nh // nkv + 15) // 16), dtype=torch.int32,
-                                                       device=a.device))
+                                                       device=dev))
             api.attention_decode_fused(qkv, o, qn, kn, cos, sin, eps, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window,
                                        s.scale, nsplit, ws_acc, ws_ml, counters, write_kv=writes)
-            return linear(o, self.w_o, ctx=ctx, allow_partial=True)
-        q = torch.empty((ctx.n_tok, nh * hd), dtype=a.dtype, device=a.device)
+            return linear(o, self.w_o, ctx=ctx, allow_partial=True, residual=residual)
+        q = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         api.qk_norm_rope_write(qkv, q, qn, kn, cos, sin, ctx.row_pos, ctx.row_seq, table, kv.k, kv.v, nh, nkv, hd, eps,
                                write_kv=writes)
-        if a.dtype == torch.float32:
+        if dtype == torch.float32:
             api.attention_generic(q, o, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, nh, nkv, hd, window, s.scale)
         elif ctx.is_decode:
             nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
             ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
-                                        lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, a.device))
+                                        lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, dev))
             api.attention_decode_bf16(q, o, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window, s.scale, nsplit,
                                       ws_acc, ws_ml)
         elif hd in api.TC_ATTENTION_HEAD_DIMS:   # tcgen05: S and P.V in tensor memory, TMA-fed
@@ -113,7 +118,7 @@ class GQAAttention(Part):
         else:
             api.attention_prefill_bf16(q, o, kv.k, kv.v, ctx.tiles, ctx.cu_q, ctx.seq_pos0, table, nh, nkv, hd,
                                        window, s.scale)
-        return linear(o, self.w_o, ctx=ctx, allow_partial=True)
+        return linear(o, self.w_o, ctx=ctx, allow_partial=True, residual=residual)
 
 
 register_part(AttentionSpec, GQAAttention)

@@ -3,11 +3,19 @@
 The residual stream ``h`` is float32. Each add is fused with the norm that follows it, so the
 block takes the previous block's not-yet-added output as ``pending`` and returns its own
 feed-forward output the same way (the reference fuses the same pair: engine/engine.py:493-495).
+
+A mixer or feed-forward that sets ``fuses_residual = True`` takes part in a further fusion: its
+``forward`` gets ``residual=h`` and may add its output into h itself (returning what
+``parts.linear.linear`` returned for its last product, a ``csrc.api.Added``), and its input may be
+a ``csrc.api.Normed``, a norm that its first product computes while loading. Parts without the
+attribute get and return plain tensors.
 """
 import torch
 
 from ..config.specs import LayerSpec
+from ..csrc import api
 from .base import ParamDecl, Part, build_part, register_part
+from .norm import RMSNorm
 
 
 class PreNormBlock(Part):
@@ -51,12 +59,22 @@ class PreNormBlock(Part):
     def forward(self, ctx, h, pending, views, writes=True, a=None):
         """``a``: norm_in(h) if the caller already has it (the embedding kernel makes it for the
         first block). Returns the feed-forward output, still to be added to h."""
+        fm = getattr(self.mixer, "fuses_residual", False)
+        ff = getattr(self.feed_forward, "fuses_residual", False)
         if a is None:
-            a = self.norm_in.add_forward(h, pending, torch.empty((h.shape[0], h.shape[1]), dtype=self.rt.dtype,
-                                                                 device=h.device))
-        d = self.mixer.forward(ctx, views, a, writes)
-        a = self.norm_post.add_forward(h, d, a)
-        return self.feed_forward.forward(ctx, a)
+            a = _add_norm(self.norm_in, h, pending, self.rt.dtype, fm)
+        d = self.mixer.forward(ctx, views, a, writes, **({"residual": h} if fm else {}))
+        a = _add_norm(self.norm_post, h, d, self.rt.dtype, ff)
+        return self.feed_forward.forward(ctx, a, **({"residual": h} if ff else {}))
+
+
+def _add_norm(norm, h, delta, dtype, may_defer):
+    """h += delta, then norm(h). Only RMSNorm knows ``csrc.api.Added`` and can defer; any other
+    norm part is called with a tensor (or None when the delta is in h already)."""
+    if isinstance(norm, RMSNorm):
+        return norm.add_forward(h, delta, dtype, defer=may_defer)
+    out = torch.empty((h.shape[0], h.shape[1]), dtype=dtype, device=h.device)
+    return norm.add_forward(h, None if isinstance(delta, api.Added) else delta, out)
 
 
 register_part(LayerSpec, PreNormBlock)

@@ -7,6 +7,8 @@ from .linear import SILU, linear
 
 
 class GatedMLP(Part):
+    fuses_residual = False   # as GQAAttention.fuses_residual
+
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         if spec.activation != "silu":
@@ -29,8 +31,9 @@ class GatedMLP(Part):
     def weights_in_order(self):
         return [self.w_gate_up, self.w_down]
 
-    def forward(self, ctx, a):
-        return linear(linear(a, self.w_gate_up, SILU, ctx, gap_follows=False), self.w_down, ctx=ctx, allow_partial=True)
+    def forward(self, ctx, a, residual=None):
+        return linear(linear(a, self.w_gate_up, SILU, ctx, gap_follows=False), self.w_down, ctx=ctx, allow_partial=True,
+                      residual=residual)
 
 
 register_part(GatedMLPSpec, GatedMLP)

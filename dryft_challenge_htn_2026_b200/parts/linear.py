@@ -12,30 +12,41 @@ from ..csrc import api
 STORE, STORE_F32, SILU = api.MODE_STORE, api.MODE_STORE_F32, api.MODE_SILU
 
 
-def linear(x, w, mode=STORE, ctx=None, gap_follows=True, allow_partial=False):
+def linear(x, w, mode=STORE, ctx=None, gap_follows=True, allow_partial=False, residual=None):
     """mode STORE: [M, N] in x's dtype; STORE_F32: float32 (logits); SILU: w = [gate; up] rows,
     returns silu(x.gate^T) * (x.up^T) of width N/2. ``ctx``: the step context; when it carries a
     weight prefetcher and short kernels follow this product (``gap_follows``), the next matrix is
     hinted into L2 behind it. ``allow_partial``: the caller can take ``csrc.api.Partial`` (split-K
-    partial sums, added up by the kernel that consumes them) instead of a tensor."""
-    out = _linear(x, w, mode, allow_partial)
+    partial sums, added up by the kernel that consumes them) instead of a tensor.
+    ``x`` may be a ``csrc.api.Normed`` (a norm of the residual stream not computed yet): the
+    streaming kernel applies it while it loads x, every other path computes it first.
+    ``residual``: the float32 residual stream this product is to be added to. Where the kernel can
+    add it in place, ``csrc.api.Added`` comes back; else the product, for the caller to add."""
+    out = _linear(x, w, mode, allow_partial, residual)
     pf = getattr(ctx, "prefetcher", None)
     if pf is not None and gap_follows:
         pf.after(w)
     return out
 
 
-def _linear(x, w, mode, allow_partial):
+def _linear(x, w, mode, allow_partial, residual):
     M, K = x.shape
     N = w.shape[0] // 2 if mode == SILU else w.shape[0]
+    if isinstance(x, api.Normed):
+        if x.dtype == torch.bfloat16 and M <= api.STREAM_MAX_ROWS and K % 16 == 0 and mode != STORE_F32:
+            plan = api.stream_plan(M, N, K, mode, allow_partial)
+            if plan is not None:
+                return api.gemv_stream(x, w, None, mode, plan)
+        x = x.tensor()
     if x.dtype == torch.float32:
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         api.sgemm(x, w, out, mode)
         return out
     if M <= api.STREAM_MAX_ROWS and K % 16 == 0:
-        plan = api.stream_plan(M, N, K, mode, allow_partial)
+        fuse = residual is not None and mode == STORE
+        plan = api.stream_plan(M, N, K, mode, allow_partial or fuse)
         if plan is not None:
-            return api.gemv_stream(x, w, None, mode, plan)
+            return api.gemv_stream(x, w, None, mode, plan, residual if fuse else None)
     if M <= api.GEMV_MAX_ROWS:
         return api.gemv_bf16(x, w, None, mode, api.gemv_plan(M, N, K, mode, allow_partial))
     if mode == STORE_F32:

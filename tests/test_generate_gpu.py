@@ -123,3 +123,30 @@ def test_engine_refuses_bad_input(tmp_path):
     with pytest.raises(ValueError):
         list(small.generate([[1] * 60], 30))
     assert len(list(small.generate([[1] * 10], 5))) == 5
+
+
+def test_products_that_add_into_the_residual_and_apply_the_deferred_norm(tmp_path, monkeypatch):
+    """The optional decode path without add+norm launches (parts opt in with fuses_residual) gives
+    the plain implementation's tokens too, and really runs the fused kernels."""
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.parts.attention import GQAAttention
+    from dryft_challenge_htn_2026_b200.parts.feedforward import GatedMLP
+    folder = make_folder(tmp_path, "D", seed=12)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY["D"]["vocab_size"], L, 40 + i) for i, L in enumerate([4, 70, 33])]
+    monkeypatch.setattr(GQAAttention, "fuses_residual", True)
+    monkeypatch.setattr(GatedMLP, "fuses_residual", True)
+    seen = {"residual": 0, "deferred": 0}
+    inner = api.gemv_stream
+
+    def counting(x, w, out=None, mode=api.MODE_STORE, plan=None, residual=None):
+        seen["residual"] += residual is not None
+        seen["deferred"] += isinstance(x, api.Normed)
+        return inner(x, w, out, mode, plan, residual)
+
+    monkeypatch.setattr(api, "gemv_stream", counting)
+    steps = list(dk.Engine(folder, dtype=torch.bfloat16, use_graph=False).generate(prompts, 16))
+    assert seen["residual"] > 0 and seen["deferred"] > 0
+    scale = max(1.0, float(plain.forward(cfg, t, prompts[1]).abs().max()))
+    for i, p in enumerate(prompts):
+        assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale

@@ -195,10 +195,13 @@ def test_attention_decode_bf16(nh, nkv, hd, window, nsplit):
     table = torch.cat([s["table"], -torch.ones(2, s["table"].shape[1], dtype=torch.int32, device=DEV)])
     out = torch.full_like(q, float("nan"))
     ws_acc, ws_ml = api.attention_decode_ws(n + 2, nh, hd, nsplit, DEV)
-    api.attention_decode_bf16(q, out, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd, window, hd ** -0.5,
-                              nsplit, ws_acc, ws_ml)
-    close(out[:n], ref_attention(q[:n], s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_decode_bf16")
-    assert float(out[n:].float().abs().max()) == 0.0                 # padding rows give zeros, not garbage
+    want = ref_attention(q[:n], s, nh, nkv, hd, window, hd ** -0.5)
+    for merge_in_kernel in (True, True, False):                      # twice in the kernel: its counters must be zero again
+        out.fill_(float("nan"))
+        api.attention_decode_bf16(q, out, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd, window, hd ** -0.5,
+                                  nsplit, ws_acc, ws_ml, merge_in_kernel)
+        close(out[:n], want, torch.bfloat16, "attention_decode_bf16")
+        assert float(out[n:].float().abs().max()) == 0.0             # padding rows give zeros, not garbage
 
 
 @pytest.mark.parametrize("kernel", ["generic_f32", "prefill", "decode"])
@@ -470,3 +473,45 @@ def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
                              hd ** -0.5)
     api.gemm_tc_check()
     close(out, ref_attention(q, s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_prefill_tc")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2560, 4096), (8, 2560, 9728), (5, 72, 304), (16, 1000, 2560), (11, 264, 5008)])
+def test_gemv_stream_adds_into_the_residual_stream(M, N, K):
+    """Product added into float32 h in place, slices meeting inside the kernel; the sums of
+    squares it leaves are those of the new h; twice, so the counters must have come back to zero."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=70), rnd(N, K, dtype=torch.bfloat16, seed=71, scale=K ** -0.5)
+    h0 = rnd(M, N, seed=72)
+    want = h0 + x.float() @ w.float().t()
+    for sk in (1, 2, 4, 8):
+        if ((K + sk - 1) // sk + 15) // 16 * 16 > 2560 or K // sk < 16:
+            continue
+        for _ in range(2):
+            h = h0.clone()
+            r = api.gemv_stream(x, w, None, api.MODE_STORE, (sk, 296), residual=h)
+            assert isinstance(r, api.Added) and r.h is h
+            err = float((h - want).abs().max())
+            assert err <= 1e-4 * max(1.0, float(want.abs().max())), f"residual, {sk} slices: {err}"   # float32 sums, other order
+            sq_err = float((r.sq.sum(0)[:M] / (h * h).sum(1) - 1).abs().max())
+            assert sq_err <= 1e-5, f"sums of squares, {sk} slices: {sq_err}"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 6144, 2560), (8, 9728, 2560), (5, 72, 304), (16, 1000, 2000), (3, 96, 5008)])
+def test_gemv_stream_applies_a_deferred_norm(M, N, K):
+    h = rnd(M, K, seed=73, scale=3.0)
+    nw = 1 + 0.2 * rnd(K, seed=74)
+    eps = 1e-5
+    sq = torch.zeros((K + 15) // 16, 16, device=DEV)
+    pad = torch.zeros(M, sq.shape[0] * 16, device=DEV)
+    pad[:, :K] = h * h
+    sq[:, :M] = pad.view(M, -1, 16).sum(2).t()
+    x = (h * torch.rsqrt((h * h).mean(1, keepdim=True) + eps) * nw).to(torch.bfloat16)
+    lazy = api.Normed(h, sq, nw, eps, torch.bfloat16)
+    close(lazy.tensor(), x.float(), torch.bfloat16, "deferred norm, computed")
+    w = rnd(N, K, dtype=torch.bfloat16, seed=75, scale=K ** -0.5)
+    plan = api.stream_plan(M, N, K, api.MODE_STORE, True)
+    r = api.gemv_stream(lazy, w, None, api.MODE_STORE, plan)
+    r = r.sum() if isinstance(r, api.Partial) else r
+    close(r, x.float() @ w.float().t(), torch.bfloat16, "deferred norm, store")
+    if N % 2 == 0 and api.stream_plan(M, N // 2, K, api.MODE_SILU) is not None:
+        g, u = (x.float() @ w.float().t()).chunk(2, dim=1)
+        close(api.gemv_stream(lazy, w, None, api.MODE_SILU), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "deferred norm, silu")
