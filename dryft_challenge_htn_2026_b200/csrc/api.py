@@ -6,6 +6,7 @@ the sizes a kernel supports); a kernel that cannot take a size raises ``KernelEr
 compute something else. There is no CPU or library fallback behind these functions.
 """
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -235,6 +236,8 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
     _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
     n_seq = q.shape[0]
+    if not 1 <= nsplit <= 32:
+        raise KernelError(f"attention_decode_bf16: {nsplit} splits, the merge takes 1 to 32")
     if nsplit > 1:
         _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
         if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * nsplit * head_dim \
@@ -371,8 +374,9 @@ def stream_plan(M, N, K, mode, allow_partial=False):
 
 class Added:
     """The result of a product that has already been added into the float32 residual stream
-    ``h`` in place. ``sq`` [ceil(width / 16), 16] float32 holds, per 16 columns, the sums of
-    squares of the new h's rows (row j in column j): what an RMSNorm of h needs."""
+    ``h`` in place. ``sq`` [pieces, 16] float32 holds the sums of squares of the new h's rows
+    (row j in column j) in pieces, one per tile of the kernel: summed over the pieces they are
+    what an RMSNorm of h needs."""
 
     def __init__(self, h, sq):
         self.h, self.sq = h, sq
@@ -430,7 +434,7 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None):
         raise KernelError(f"gemv_stream: {M} rows (max {STREAM_MAX_ROWS}) / inner size {K} (multiple of 16) not supported")
     if w.shape[1] != K:
         raise KernelError(f"gemv_stream: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
-    if lazy and (x.sq.shape[0] != (K + 15) // 16 or x.sq.shape[1] != 16 or x.weight.numel() != K):
+    if lazy and (x.sq.shape[1] != 16 or x.weight.numel() != K):
         raise KernelError("gemv_stream: the deferred norm's sums of squares or weight do not fit the input width")
     if residual is not None and (mode != MODE_STORE or tuple(residual.shape) != (M, N)):
         raise KernelError("gemv_stream: a residual goes with mode STORE and has the output's shape")
@@ -554,3 +558,24 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
                                        c_float(scale), _p(_tc_err), _stream()), "attention_prefill_tc")
+
+
+def kernel_trace():
+    """Development (needs DRYFT_KERNEL_TRACE=1 in the environment before the first import): the
+    notes the kernels launched since the last call left, as a time-ordered list of
+    (nanoseconds, source file, blocks, threads per block); each is the moment the kernel's wait for
+    its predecessor ended."""
+    import ctypes
+
+    from . import build
+    if not build.TRACE:
+        raise KernelError("kernel_trace: set DRYFT_KERNEL_TRACE=1 before importing the package")
+    events = []
+    for (source, _), lib in build.loaded_libs().items():
+        if not hasattr(lib, "dk_trace_read"):
+            continue
+        t = (ctypes.c_ulonglong * 8192)()
+        sig = (ctypes.c_ulonglong * 8192)()
+        n = lib.dk_trace_read(t, sig, 8192)
+        events += [(t[i], source, sig[i] >> 32, sig[i] & 0xffffffff) for i in range(max(0, n))]
+    return sorted(events)

@@ -239,8 +239,6 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
                    int* counters) {
     extern __shared__ __align__(16) bf16 smem[];
     __shared__ int is_last;
-    pdl_wait();
-    pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
     const int split = blockIdx.x, nsplit = gridDim.x;
@@ -248,40 +246,51 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
     const int b = blockIdx.z;
     const int head0 = kvh * G + mt * 16;
     const int heads_here = min(16, G - mt * 16);
+    // Positions and page tables are not written by the kernel before this one, and of the cache
+    // only the page of the newest token is (its key and value were just stored): the first page of
+    // this block, unless it is that one, is requested before the wait for that kernel.
     const int pos = row_pos[b];
     const int* pt = page_table + (size_t)b * pt_stride;
+    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
+    const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
+    const int jt0 = t_lo + split * per, jt1 = min(t_hi + 1, jt0 + per);  // [jt0, jt1)
+    const bool any = pos >= 0 && jt0 < jt1;
+    const bool early = any && jt0 < t_hi;
+    if (early) {
+        stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
+        cp_async_commit();
+    }
+    pdl_wait();
+    pdl_launch_dependents();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float acc[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-    if (pos >= 0) {
-        const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
-        const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
-        const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
-        const int jt0 = t_lo + split * per, jt1 = min(t_hi + 1, jt0 + per);  // [jt0, jt1)
-        if (jt0 < jt1) {
-            uint32_t qf[HD / 16][4];
-            const bf16* qb = q + ((size_t)b * nh + head0) * HD;
-            load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
-                         g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
-            const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
+    if (any) {
+        uint32_t qf[HD / 16][4];
+        const bf16* qb = q + ((size_t)b * nh + head0) * HD;
+        load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
+                     g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
+        const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
+        if (!early) {
             stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
             cp_async_commit();
-            for (int jt = jt0; jt < jt1; jt++) {
-                const int cur = (jt - jt0) & 1;
-                if (jt + 1 < jt1) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
-                cp_async_commit();
-                cp_async_wait<1>();
-                __syncthreads();
-                const int key0 = jt * DK_PAGE + warp * 16;
-                if (key0 <= pos && key0 + 15 >= key_lo) {
-                    const bf16* Ks = smem + cur * STAGE_ELEMS + warp * 16 * KSTR;
-                    warp_attend<16>(qf, Ks, Ks + TILE_ELEMS, key0, lo, hi, sl2, m, l, acc);
-                }
-                __syncthreads();
+        }
+        for (int jt = jt0; jt < jt1; jt++) {
+            const int cur = (jt - jt0) & 1;
+            if (jt + 1 < jt1) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+            const int key0 = jt * DK_PAGE + warp * 16;
+            if (key0 <= pos && key0 + 15 >= key_lo) {
+                const bf16* Ks = smem + cur * STAGE_ELEMS + warp * 16 * KSTR;
+                warp_attend<16>(qf, Ks, Ks + TILE_ELEMS, key0, lo, hi, sl2, m, l, acc);
             }
+            __syncthreads();
         }
     }
     cp_async_wait<0>();
@@ -381,23 +390,53 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
     }
 }
 
-// grid (sequences * nh), HD threads or fewer looping: merges the splits of one head.
-__global__ void attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int nsplit) {
+// grid (sequences * nh / 4), 128 threads: a warp merges the splits of one head. Lane s holds split
+// s's (max, sum); the partial outputs of the first 8 splits are requested together with them, so
+// up to 8 splits cost one trip to memory after the wait (nsplit <= 32).
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int nsplit, int n_heads) {
     pdl_wait();
     pdl_launch_dependents();
-    const size_t head = blockIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; s++) M = fmaxf(M, ws_ml[(head * nsplit + s) * 2]);
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
-        float L = 0.f, A = 0.f;
-        if (M != -INFINITY) {
-            for (int s = 0; s < nsplit; s++) {
-                const float f = exp2f(ws_ml[(head * nsplit + s) * 2] - M);
-                L += ws_ml[(head * nsplit + s) * 2 + 1] * f;
-                A += ws_acc[(head * nsplit + s) * HD + d] * f;
+    const int lane = threadIdx.x & 31;
+    const size_t head = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (head >= (size_t)n_heads) return;
+    const float* ml = ws_ml + head * nsplit * 2;
+    const float* wa = ws_acc + head * nsplit * HD;
+    const float Ms = lane < nsplit ? ml[2 * lane] : -INFINITY;
+    const float Ls = lane < nsplit ? ml[2 * lane + 1] : 0.f;
+    float fs = 0.f, inv = 0.f;
+    for (int base = 0; base < HD; base += 128) {
+        const int d0 = base + lane * 4;
+        const bool ok = d0 < HD;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < nsplit; s0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                v[u] = ok && s0 + u < nsplit ? *reinterpret_cast<const float4*>(wa + (size_t)(s0 + u) * HD + d0)
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (base == 0 && s0 == 0) {       // the weights of the splits, once
+                float M = Ms;
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+                fs = M == -INFINITY ? 0.f : exp2f(Ms - M);
+                float L = Ls * fs;
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
+                inv = L > 0.f ? 1.f / L : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const float f = __shfl_sync(0xffffffffu, fs, (s0 + u) & 31);
+                a.x += v[u].x * f, a.y += v[u].y * f, a.z += v[u].z * f, a.w += v[u].w * f;
             }
         }
-        out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
+        if (ok) {
+            uint2 o;
+            o.x = pack_bf16(a.x * inv, a.y * inv);
+            o.y = pack_bf16(a.z * inv, a.w * inv);
+            *reinterpret_cast<uint2*>(out + head * HD + d0) = o;
+        }
     }
 }
 
@@ -432,7 +471,7 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
                                   const void* v_store, const int* row_pos, const int* page_table, int pt_stride,
                                   int n_seq, int nh, int nkv, int window, float scale, int nsplit, int* counters,
                                   cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1 || (counters != nullptr && nsplit > 32)) return (int)cudaErrorInvalidValue;
+    if (nh % nkv != 0 || nsplit < 1 || nsplit > 32) return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
@@ -440,8 +479,8 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
                   (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
                   nh, nkv, window, scale * 1.4426950408889634f, counters);
     if (e || nsplit == 1 || counters != nullptr) return e;   // (callers give counters only for nsplit <= 32)
-    return dk_launch(attn_combine_kernel, dim3(n_seq * nh), dim3(HD < 128 ? HD : 128), 0, st, (const float*)ws_acc,
-                     (const float*)ws_ml, (bf16*)out, nsplit);
+    return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
+                     (const float*)ws_ml, (bf16*)out, nsplit, n_seq * nh);
 }
 
 // ------------------------------------------------------------------------------- fused decode

@@ -19,6 +19,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD_DIR = os.path.join(HERE, "_build")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# development: DRYFT_KERNEL_TRACE=1 builds (separately named) objects whose kernels note when they
+# start; csrc.api.kernel_trace() reads the notes
+TRACE = os.environ.get("DRYFT_KERNEL_TRACE", "") not in ("", "0")
+if TRACE:
+    NVCC_FLAGS.append("-DDK_TRACE")
 
 _libs = {}
 _lock = threading.Lock()
@@ -95,6 +100,11 @@ def load_lib(source, defines=None):
             lib = ctypes.CDLL(compile_lib(source, defines))
             _libs[key] = lib
     return lib
+
+
+def loaded_libs():
+    """{(source, defines): handle} of the objects loaded so far."""
+    return dict(_libs)
 
 
 def build_all(head_dims=(16, 32, 64, 128), verbose=False):

@@ -71,6 +71,59 @@ __global__ void add_rmsnorm_kernel(float* h, const T* delta, const float* parts,
     for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(src[i] * rs * w[i]);
 }
 
+// The same for few rows (decode), built for latency: one block per row, one thread per 4 columns,
+// values kept in registers between the two passes, every load of a pass requested before any is
+// used, and what never comes from the kernel before this one (norm weight, row index) fetched
+// before the wait for it. H % 4 == 0, H <= 4096.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&lo);
+    o.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+template <typename T>
+__global__ void add_rmsnorm_quad_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride,
+                                        const int* rows, const float* __restrict__ w, float eps, int H, T* a) {
+    __shared__ float red[33];
+    const int c = threadIdx.x * 4;
+    const bool on = c < H;
+    const size_t out_row = blockIdx.x;
+    const size_t row = rows ? (size_t)rows[out_row] : out_row;
+    const float4 w4 = on ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    pdl_wait();
+    pdl_launch_dependents();
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) {
+        v = ld4(h + row * H + c);
+        if (delta) {
+            const float4 d = ld4(delta + row * H + c);
+            v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+        }
+        if (parts) {
+            float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+            for (int k = 0; k < n_parts; k++) {
+                const float4 p = ld4(parts + (size_t)k * part_stride + row * H + c);
+                d.x += p.x, d.y += p.y, d.z += p.z, d.w += p.w;
+            }
+            v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+        }
+        if (!rows && (delta || parts)) st4(h + row * H + c, v);
+    }
+    const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    if (on) st4(a + out_row * H + c, make_float4(v.x * rs * w4.x, v.y * rs * w4.y, v.z * rs * w4.z, v.w * rs * w4.w));
+}
+
 // out[r, c] = silu(gu[r, c]) * gu[r, I + c],  gu rows are [gate | up] of width 2*I
 template <typename T>
 __global__ void silu_mul_kernel(const T* gu, T* out, size_t n, int I) {
@@ -101,60 +154,77 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int 
                                           const int* page_table, int pt_stride,
                                           T* k_store, T* v_store, int n_tok, int nh,
                                           int nkv, int hd, float eps, int write_kv) {
-    pdl_wait();
-    pdl_launch_dependents();
+    // Positions, page ids, angles and norm weights never come from the kernel before this one (the
+    // projection): they are fetched before the wait for it, and the projection row in one batch
+    // after it, so that the wait is followed by one trip to memory, not five.
     const int lane = threadIdx.x & 31;
     const int heads = nh + 2 * nkv;
     const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= (long long)n_tok * heads) return;
-    const int t = (int)(wid / heads), hidx = (int)(wid % heads);
-    const int pos = row_pos[t];
-    if (pos < 0) return;
+    const bool live = wid < (long long)n_tok * heads;
+    const int t = live ? (int)(wid / heads) : 0, hidx = live ? (int)(wid % heads) : 0;
+    const int pos = live ? row_pos[t] : -1;
     const int half = hd >> 1;
-    const size_t x_off = (size_t)t * heads * hd + (size_t)hidx * hd;
-    auto xin = [&](int d) {
-        if (parts == nullptr) return to_f(qkv[x_off + d]);
-        float s = 0.f;
-        for (int k = 0; k < n_parts; k++) s += parts[(size_t)k * part_stride + x_off + d];
-        return s;
-    };
-
-    T* dst;
-    if (hidx < nh) {
-        dst = q_out + ((size_t)t * nh + hidx) * hd;
-    } else {
-        if (!write_kv) return;
-        const int kvh = (hidx - nh) % nkv;
-        const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
-        T* store = hidx < nh + nkv ? k_store : v_store;
-        dst = store + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+    const bool is_q = hidx < nh, is_v = hidx >= nh + nkv;
+    const bool work = pos >= 0 && (is_q || write_kv);
+    T* dst = nullptr;
+    if (work) {
+        if (is_q) {
+            dst = q_out + ((size_t)t * nh + hidx) * hd;
+        } else {
+            const int kvh = (hidx - nh) % nkv;
+            const int page = page_table[(size_t)row_seq[t] * pt_stride + pos / DK_PAGE];
+            dst = (is_v ? v_store : k_store) + kv_offset(page, nkv, kvh, pos % DK_PAGE, hd);
+        }
     }
-    if (hidx >= nh + nkv) {  // value head: plain copy
-        for (int d = lane; d < hd; d += 32) dst[d] = from_f<T>(xin(d));
-        return;
-    }
-    // pairs (d, d + half), d = lane + 32*i; hd <= 256 gives at most 4 pairs a lane
-    float x1[4], x2[4];
-    float ss = 0.f;
+    const float* nw = is_q ? qn : kn;
+    float c[4], sn[4], w1[4], w2[4];   // pairs (d, d + half), d = lane + 32*i; hd <= 256 gives at most 4 pairs a lane
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const int d = lane + 32 * i;
-        x1[i] = d < half ? xin(d) : 0.f;
-        x2[i] = d < half ? xin(d + half) : 0.f;
-        ss += x1[i] * x1[i] + x2[i] * x2[i];
+        const bool on = work && !is_v && d < half;
+        c[i] = on && cos_t ? cos_t[(size_t)pos * half + d] : 1.f;
+        sn[i] = on && cos_t ? sin_t[(size_t)pos * half + d] : 0.f;
+        w1[i] = on && nw ? nw[d] : 1.f;
+        w2[i] = on && nw ? nw[d + half] : 1.f;
     }
-    const float* nw = hidx < nh ? qn : kn;
-    if (nw) {
-        ss = warp_sum(ss);
-        const float rs = rsqrtf(ss / (float)hd + eps);
+    pdl_wait();
+    pdl_launch_dependents();
+    if (!work) return;
+    const size_t x_off = (size_t)t * heads * hd + (size_t)hidx * hd;
+    float x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
+    if (parts == nullptr) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int d = lane + 32 * i;
-            if (d < half) {
-                x1[i] = x1[i] * rs * nw[d];
-                x2[i] = x2[i] * rs * nw[d + half];
+            if (d < half) x1[i] = to_f(qkv[x_off + d]), x2[i] = to_f(qkv[x_off + d + half]);
+        }
+    } else {
+#pragma unroll 4
+        for (int k = 0; k < n_parts; k++) {
+            const float* pk = parts + (size_t)k * part_stride + x_off;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int d = lane + 32 * i;
+                if (d < half) x1[i] += pk[d], x2[i] += pk[d + half];
             }
         }
+    }
+    if (is_v) {  // value head: plain copy
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int d = lane + 32 * i;
+            if (d < half) dst[d] = from_f<T>(x1[i]), dst[d + half] = from_f<T>(x2[i]);
+        }
+        return;
+    }
+    if (nw) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) ss += x1[i] * x1[i] + x2[i] * x2[i];
+        ss = warp_sum(ss);
+        const float rs = rsqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < 4; i++) x1[i] = x1[i] * rs * w1[i], x2[i] = x2[i] * rs * w2[i];
     }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -162,9 +232,8 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int 
         if (d < half) {
             float o1 = x1[i], o2 = x2[i];
             if (cos_t) {
-                const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
-                o1 = x1[i] * c - x2[i] * s;
-                o2 = x2[i] * c + x1[i] * s;
+                o1 = x1[i] * c[i] - x2[i] * sn[i];
+                o2 = x2[i] * c[i] + x1[i] * sn[i];
             }
             dst[d] = from_f<T>(o1);
             dst[d + half] = from_f<T>(o2);
@@ -350,6 +419,10 @@ DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float
     if (dtype == 1 && parts == nullptr && rows == nullptr && H % 8 == 0 && H <= 8 * 4 * row_threads(H) && n_rows > 64)
         return dk_launch(add_rmsnorm_wide_kernel, dim3(n_rows), dim3(row_threads(H)), 0, st, h, (const bf16*)delta, w, eps,
                          H, (bf16*)a);
+    if (n_rows <= 64 && H % 4 == 0 && H <= 4096 && part_stride % 4 == 0) {
+        DISPATCH_T(dtype, return dk_launch(add_rmsnorm_quad_kernel<T>, dim3(n_rows), dim3((H / 4 + 31) / 32 * 32), 0, st, h,
+                                           (const T*)delta, parts, n_parts, (size_t)part_stride, rows, w, eps, H, (T*)a));
+    }
     size_t smem = rows ? (size_t)H * sizeof(float) : 0;
     if (smem > 48 * 1024) {
         DISPATCH_T(dtype, cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,

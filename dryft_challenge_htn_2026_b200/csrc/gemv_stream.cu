@@ -33,6 +33,21 @@
 // Requires K % 16 == 0, 16-byte aligned x and W, a slice of at most XMAX elements.
 #include "common.cuh"
 
+#ifdef DK_TRACE
+__device__ unsigned long long gs_phase[4][8];
+__device__ __forceinline__ void gs_note(int ph) {
+    if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == 100 || blockIdx.x == 200 || blockIdx.x == 295)) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        gs_phase[blockIdx.x / 100 > 2 ? 3 : blockIdx.x / 100][ph] = t;
+    }
+}
+DK_EXPORT int dk_gs_phases(unsigned long long* out) { cudaDeviceSynchronize(); return (int)cudaMemcpyFromSymbol(out, gs_phase, sizeof(gs_phase)); }
+#define GS_NOTE(p) gs_note(p)
+#else
+#define GS_NOTE(p)
+#endif
+
 namespace {
 
 constexpr int STAGE_K = 256;                  // elements of K per stage
@@ -49,6 +64,13 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool r
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(real ? 16 : 0) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// 16-byte load that stays where it is written: the compiler keeps volatile asm in order, so a run
+// of these is in flight together instead of each sinking to its use
+__device__ __forceinline__ float4 ld_cg_f4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
@@ -71,7 +93,7 @@ __host__ __device__ __forceinline__ int slice_len(int K, int SK) { return ((K + 
 
 struct Fuse {
     const float* h_in;    // FUSE 1: residual stream [M,K]
-    const float* sq_in;   //         [sq_tiles][16] sums of squares of its rows, one line per 16 columns
+    const float* sq_in;   //         [sq_tiles][16] sums of squares of its rows, in any number of pieces
     const float* norm_w;  //         [K]
     float eps;
     int sq_tiles;
@@ -83,6 +105,8 @@ struct Fuse {
 // MR: rows of x kept (8 or 16, M <= MR). MODE as in gemm.cu. Mode 2: a tile's rows 0-7 are the
 // gate rows of 8 outputs and rows 8-15 their up rows, so a tile covers 8 outputs.
 // gridDim.x is a multiple of SK: block b has slice b % SK and tiles b / SK, + gridDim.x / SK, ...
+// (Dealing the rows out evenly instead, in tiles of unequal heights, was measured 15 % slower: the
+// bytes a ring slot holds in flight shrink with the tile, and the kernel lives on bytes in flight.)
 template <int MR, int MODE, int FUSE>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK,
@@ -128,54 +152,76 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         if (head < total) fetch(head, d);
         cp_async_commit();
     }
+    GS_NOTE(0);
     pdl_wait();
+    GS_NOTE(1);
     if (tid == 0) pdl_launch_dependents();
     // x rows of this block's slice, once
     if (FUSE == 1) {
-        constexpr int U = 20;                 // float4 loads in flight per thread
-        const int row_quads = klen / 4;       // 4 floats in, 8 bytes out
-        const int total = M * row_quads;
-        float4 hv[U];
+        // A thread owns columns (groups of 4) tid, tid + 128, ... of the slice for all M rows: the
+        // norm weight of a column is loaded once, and a batch of CG columns x (M rows + weight) is
+        // requested before anything is used, so a batch costs one trip to L2, not one per load.
+        constexpr int CG = MR == 8 ? 3 : 2;
+        const int row_quads = klen / 4;
+        float ssr[MR / WARPS];
 #pragma unroll
-        for (int u = 0; u < U; u++) {         // the first batch goes out before the sums of squares are awaited
-            const int c = tid + u * WARPS * 32;
-            if (c < total) hv[u] = __ldcg(reinterpret_cast<const float4*>(fu.h_in + (size_t)(c / row_quads) * K + k_begin + (c % row_quads) * 4));
-        }
-        for (int j = warp; j < M; j += WARPS) {
+        for (int r = 0; r < MR / WARPS; r++) {   // sums of squares: warp w has rows w, w + 4, ...
+            const int j = warp + r * WARPS;
             float ss = 0.f;
+            if (j < M)
 #pragma unroll 8
-            for (int i = lane; i < fu.sq_tiles; i += 32) ss += __ldcg(fu.sq_in + i * 16 + j);
-            ss = warp_sum(ss);
-            if (lane == 0) rstd_s[j] = rsqrtf(ss / (float)K + fu.eps);
+                for (int i = lane; i < fu.sq_tiles; i += 32) ss += __ldcg(fu.sq_in + i * 16 + j);
+            ssr[r] = ss;
         }
-        __syncthreads();
-        for (int base = 0; base < total; base += U * WARPS * 32) {
+        float4 hv[CG][MR], wv[CG];
+        auto request = [&](int q0) {
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int c = base + tid + u * WARPS * 32;
-                if (c < total) {
-                    const int m = c / row_quads, j = c % row_quads;
-                    const float4 wv = *reinterpret_cast<const float4*>(fu.norm_w + k_begin + j * 4);
-                    const float rs = rstd_s[m];
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(hv[u].x * rs * wv.x, hv[u].y * rs * wv.y);
-                    __nv_bfloat162 hi = __floats2bfloat162_rn(hv[u].z * rs * wv.z, hv[u].w * rs * wv.w);
-                    uint2 pk;
-                    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-                    pk.y = *reinterpret_cast<uint32_t*>(&hi);
-                    *reinterpret_cast<uint2*>(xs + m * x_stride + j * 8) = pk;
+            for (int c = 0; c < CG; c++) {
+                const int q = q0 + c * WARPS * 32;
+                if (q < row_quads) {
+                    wv[c] = ld_cg_f4(fu.norm_w + k_begin + q * 4);
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (m < M) hv[c][m] = ld_cg_f4(fu.h_in + (size_t)m * K + k_begin + q * 4);
                 }
             }
-            const int next = base + U * WARPS * 32;
+        };
+        request(tid);
 #pragma unroll
-            for (int u = 0; u < U; u++) {
-                const int c = next + tid + u * WARPS * 32;
-                if (c < total) hv[u] = __ldcg(reinterpret_cast<const float4*>(fu.h_in + (size_t)(c / row_quads) * K + k_begin + (c % row_quads) * 4));
-            }
+        for (int r = 0; r < MR / WARPS; r++) {
+            const float ss = warp_sum(ssr[r]);
+            if (lane == 0 && warp + r * WARPS < M) rstd_s[warp + r * WARPS] = rsqrtf(ss / (float)K + fu.eps);
         }
+        __syncthreads();
+        for (int q0 = tid; q0 < row_quads; q0 += CG * WARPS * 32) {
+#pragma unroll
+            for (int c = 0; c < CG; c++) {
+                const int q = q0 + c * WARPS * 32;
+                if (q < row_quads) {
+#pragma unroll
+                    for (int m = 0; m < MR; m++)
+                        if (m < M) {
+                            const float rs = rstd_s[m];
+                            const float4 h4 = hv[c][m], w4 = wv[c];
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(h4.x * rs * w4.x, h4.y * rs * w4.y);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(h4.z * rs * w4.z, h4.w * rs * w4.w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                            pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                            *reinterpret_cast<uint2*>(xs + m * x_stride + q * 8) = pk;
+                        }
+                }
+            }
+            request(q0 + CG * WARPS * 32);
+        }
+        cp_async_wait<0>();                   // the first weight stages, fetched before the wait
         __syncthreads();
     } else {
         const int row_chunks = klen / 8;      // 16-byte chunks per row
-        for (int c = tid; c < M * row_chunks; c += WARPS * 32) {
+        const int total = M * row_chunks;
+        const int rot = (int)(((long long)blockIdx.x * total) / gridDim.x) & ~31;   // see above: spread the blocks over L2
+        for (int c0 = tid; c0 < total; c0 += WARPS * 32) {
+            const int c = c0 + rot < total ? c0 + rot : c0 + rot - total;
             const int m = c / row_chunks, j = c % row_chunks;
             cp_async16(smem_u32(xs + m * x_stride + j * 16), x + (size_t)m * K + k_begin + j * 8, true);
         }
@@ -184,6 +230,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         __syncthreads();
     }
 
+    GS_NOTE(2);
     float acc[2][NT][4];
 #pragma unroll
     for (int h = 0; h < 2; h++)
@@ -306,6 +353,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         __syncthreads();
     }
     cp_async_wait<0>();
+    GS_NOTE(3);
 }
 
 template <int MR, int MODE, int FUSE>
