@@ -501,22 +501,69 @@ def attention_decode_fused(qkv, out, q_norm_w, k_norm_w, cos, sin, eps, k_store,
 _tc_err = None
 
 
-def gemm_tc(x, w, mode=MODE_STORE, out=None):
-    """out = x . w^T (mode MODE_STORE) or silu(x . gate^T) * (x . up^T) (mode MODE_SILU, w = [gate;
-    up]) on tcgen05 tensor cores, TMA-fed, float32 accumulation in tensor memory, bfloat16 out."""
+def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
+    """out = x . w^T (mode MODE_STORE, MODE_STORE_F32) or silu(x . gate^T) * (x . up^T) (mode
+    MODE_SILU, w = [gate; up]) on tcgen05 tensor cores, TMA-fed, float32 accumulation in tensor
+    memory. ``plan`` = (weight rows per tile: 128 or 256, for MODE_SILU also 144, 160 and 192;
+    slices of K): with more than one slice (mode MODE_STORE) a ``Partial`` comes back instead of a
+    tensor."""
     global _tc_err
-    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
     M, K = x.shape
     N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
-    if K % 8 or w.shape[1] != K or mode not in (MODE_STORE, MODE_SILU):
+    bn, sk = plan or (256, 1)
+    if K % 8 or w.shape[1] != K or mode not in (MODE_STORE, MODE_STORE_F32, MODE_SILU) \
+            or bn not in ((128, 144, 160, 192, 256) if mode == MODE_SILU else (128, 256)):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} mode {mode} not supported (K % 8 == 0)")
-    if out is None:
+    kb = (K + 63) // 64
+    if sk < 1 or (sk > 1 and (mode != MODE_STORE or (sk - 1) * ((kb + sk - 1) // sk) >= kb)):
+        raise KernelError(f"gemm_tc: {sk} slices of K = {K} in mode {mode} not supported")
+    ws = None
+    if sk > 1:
+        ws = torch.empty((sk, M, N), dtype=torch.float32, device=x.device)
+    elif mode == MODE_STORE_F32:
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        ws = out
+    elif out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
+    if sk == 1 and (out.dtype != want or tuple(out.shape) != (M, N)):
+        raise KernelError(f"gemm_tc: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
     if _tc_err is None:
         _tc_err = torch.zeros(1, dtype=torch.int32, device=x.device)
     lib = _lib("gemm_tc.cu")
-    _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(out), M, N, K, mode, _p(_tc_err), _stream()), "gemm_tc")
-    return out
+    _check(lib, lib.dk_gemm_tc(_p(x), _p(w), _p(None if ws is not None else out), M, N, K,
+                               MODE_STORE if mode == MODE_STORE_F32 else mode, _p(_tc_err), sk, _p(ws), bn, _stream()),
+           "gemm_tc")
+    return Partial(ws) if sk > 1 else out
+
+
+TC_SKINNY_MAX_ROWS = 128
+
+
+def skinny_tc_plan(M, N, K, mode, allow_partial=False):
+    """(weight rows per tile, slices of K) for gemm_tc on a decode step of up to 128 rows: one
+    block per unit (tile, slice), as many units as fit the SMs, slices of at least 8 blocks of 64
+    columns (fewer cannot keep the load ring busy), fewer slices on a tie."""
+    kb = (K + 63) // 64
+    if mode == MODE_SILU:      # no slices (SiLU needs whole sums): the tile width that covers most SMs
+        def fill(bn):
+            tiles = (N + bn // 2 - 1) // (bn // 2)
+            return tiles / (-(-tiles // SM_COUNT) * SM_COUNT)
+        return max((256, 192, 160, 144, 128), key=fill), 1
+    if mode != MODE_STORE or not allow_partial:
+        return 256, 1
+    best = None
+    for bn in (256, 128):
+        tiles = (N + bn - 1) // bn
+        sk = max(1, min(SM_COUNT // tiles, kb // 8))
+        while sk > 1 and (sk - 1) * ((kb + sk - 1) // sk) >= kb:
+            sk -= 1
+        key = (min(tiles * sk, SM_COUNT), -sk)
+        if best is None or key > best[0]:
+            best = (key, (bn, sk))
+    return best[1]
 
 
 def gemm_tc_fills_gpu(M, N, min_fill=0.8):

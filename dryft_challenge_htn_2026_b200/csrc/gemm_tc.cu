@@ -19,13 +19,21 @@
 // Rows of x beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA; stores are
 // masked. K must be a multiple of 8 (16-byte global strides). Every mbarrier wait is bounded: if
 // one runs out the block stores a code in *err, still frees its tensor memory, and returns.
+//
+// The same kernel serves decode steps of 17 to 128 rows, where the weights are the traffic and a
+// few tiles cannot fill the GPU: K is cut into SK slices, a unit of work is (tile, slice), and the
+// float32 partial sums of a unit go to ws [SK][M][N] for the consumer to add up (mode 0). There
+// the producer requests the weight tiles of its first stages before it waits for the previous
+// kernel (weights never depend on it) and the rows of x after.
 #include <cuda.h>
 
 #include "common.cuh"
 
 namespace {
 
-constexpr int BM = 128, BK = 64, STAGES = 4;
+constexpr int BM = 128, BK = 64;
+// stages of the load ring for BN weight rows a tile: as many as fit in about 200 KB, at most 8
+__host__ __device__ constexpr int stages_for(int bn) { return (200 * 1024) / (BM * BK * 2 + bn * BK * 2) > 8 ? 8 : (200 * 1024) / (BM * BK * 2 + bn * BK * 2); }
 constexpr int A_BYTES = BM * BK * 2;
 constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
 
@@ -90,9 +98,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 template <int BN, int MODE>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, bf16* out, int M,
-               int N, int K, int m_tiles, int tiles, int* err) {
+               int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws) {
     constexpr int B_BYTES = BN * BK * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int STAGES = stages_for(BN);
+    constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators; allocations are powers of two
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;   // outputs per tile
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
@@ -104,8 +114,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (K + BK - 1) / BK;
+    const int k_per = (k_blocks + SK - 1) / SK;   // k blocks per slice; unit u = (tile u / SK, slice u % SK)
+    const int units = tiles * SK;
+    const bool early_w = SK > 1 || ws != nullptr || m_tiles == 1;   // decode: weights before the wait
 
-    pdl_wait();
+    if (!early_w) pdl_wait();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
@@ -119,7 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -130,19 +143,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {  // ------------------------------------------------------------ producer
-            int it = 0;   // stages issued so far, over all tiles of this block
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            int it = 0;   // stages issued so far, over all units of this block
+            bool waited = !early_w;
+            int early_kb[STAGES], early_m0[STAGES];   // stages whose rows of x are still to be requested
+            auto flush = [&](int n) {                 // the previous kernel's output may be read from here on
+                pdl_wait();
+                pdl_launch_dependents();
+                waited = true;
+                for (int j = 0; j < n; j++) tma_load_2d(smem + j * STAGE_BYTES, &map_x, early_kb[j] * BK, early_m0[j], &full[j]);
+            };
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+                const int tile = unit / SK, slice = unit % SK;
                 const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
-                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                const int kb0 = slice * k_per, kb1 = min(k_blocks, kb0 + k_per);
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
+                    if (!waited && it == STAGES) flush(STAGES);   // the ring is full of weights
                     if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
                         atomicExch(err, 1);
-                        tile = tiles;
+                        unit = units;
                         break;
                     }
                     uint8_t* stage = smem + s * STAGE_BYTES;
                     mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
+                    if (waited) {
+                        tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
+                    } else {
+                        early_kb[it] = kb;
+                        early_m0[it] = m0;
+                    }
                     if (MODE == 2) {
                         tma_load_2d(stage + A_BYTES, &map_w, kb * BK, n0, &full[s]);
                         tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
@@ -151,12 +180,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                 }
             }
+            if (!waited) flush(it);
         }
     } else if (warp == 1) {
         if (lane == 0) {  // ---------------------------------------------------------- mma issuer
             int it = 0, iter = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, iter++) {
+            for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, iter++) {
+                const int slice = unit % SK;
+                const int kb0 = slice * k_per, kb1 = min(k_blocks, kb0 + k_per);
                 const int buf = iter & 1;
                 if (iter >= 2 && !mbar_wait(&acc_empty[buf], ((iter >> 1) & 1) ^ 1)) {   // the epilogue has drained it
                     atomicExch(err, 4);
@@ -165,7 +197,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem + buf * BN;
-                for (int kb = 0; kb < k_blocks; kb++, it++) {
+                for (int kb = kb0; kb < kb1; kb++, it++) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
                         atomicExch(err, 2);
@@ -176,7 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)
-                        umma_f16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb | k) != 0);
+                        umma_f16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb > kb0) | (k != 0));
                     umma_commit(&empty[s]);   // the stage is free once these mma have read it
                 }
                 umma_commit(&acc_full[buf]);  // arrives when every mma above has finished
@@ -185,7 +217,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else {  // -------------------------------------------------------------------------- epilogue
         const int q = warp & 3;               // the quarter of the tensor-memory lanes this warp may read
         int iter = 0;
-        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, iter++) {
+        if (early_w) pdl_wait();              // nothing is stored before the previous kernel is done
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, iter++) {
+            const int tile = unit / SK, slice = unit % SK;
             const int buf = iter & 1;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
             const int row = m0 + q * 32 + lane;
@@ -208,9 +242,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; i++) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
                 }
-                if (row < M) {
+                if (row < M && ws != nullptr) {   // float32 partial sums of this slice
+                    float* dst = ws + ((size_t)slice * M + row) * N + n0 + c;
+                    if (n0 + c + 32 <= N && c + 32 <= OUT_COLS && (N % 4 == 0)) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(f[i], f[i + 1], f[i + 2], f[i + 3]);
+                    } else {
+                        for (int i = 0; i < 32; i++)
+                            if (n0 + c + i < N && c + i < OUT_COLS) dst[i] = f[i];
+                    }
+                } else if (row < M) {
                     bf16* dst = out + (size_t)row * N + n0 + c;
-                    if (n0 + c + 32 <= N && (N % 8 == 0)) {
+                    if (n0 + c + 32 <= N && c + 32 <= OUT_COLS && (N % 8 == 0)) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
                             uint4 pk;
@@ -221,7 +264,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         }
                     } else {
                         for (int i = 0; i < 32; i++)
-                            if (n0 + c + i < N) dst[i] = __float2bfloat16_rn(f[i]);
+                            if (n0 + c + i < N && c + i < OUT_COLS) dst[i] = __float2bfloat16_rn(f[i]);
                     }
                 }
             }
@@ -235,10 +278,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // ---- teardown: everyone arrives, then the allocating warp frees the tensor memory
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    pdl_launch_dependents();
+    if (!early_w) pdl_launch_dependents();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -273,8 +316,9 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }
 
 template <int BN, int MODE>
-int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, cudaStream_t st) {
+int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, int SK, float* ws, cudaStream_t st) {
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;
+    constexpr int STAGES = stages_for(BN);
     constexpr size_t smem = 1024 + (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
     static bool attr = false;
     if (!attr) {
@@ -288,21 +332,35 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
     e = make_map(&mw, W, MODE == 2 ? 2LL * N : N, K, MODE == 2 ? BN / 2 : BN);
     if (e) return e;
     const int m_tiles = (M + BM - 1) / BM, tiles = m_tiles * ((N + OUT_COLS - 1) / OUT_COLS);
+    const int units = tiles * SK;
     int sms = 0, dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(tiles < sms ? tiles : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
-                     m_tiles, tiles, err);
+    return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(units < sms ? units : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
+                     m_tiles, tiles, err, SK, ws);
 }
 
 }  // namespace
 
 // x [M,K] bf16, W [N,K] bf16 (mode 2: [2N,K] = gate rows then up rows), out [M,N] bf16.
 // err: device int, receives a code if a bounded wait ran out. K % 8 == 0; 16-byte aligned x, W.
-DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, cudaStream_t st) {
-    if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr) return (int)cudaErrorInvalidValue;
+// ws != null (mode 0): float32 results into ws [SK][M][N] instead of out, the partial sums of SK
+// slices of K (every slice at least one block of 64 columns; SK = 1: the product itself in
+// float32). bn: weight rows a tile, 128 or 256 (mode 2 also 144, 160, 192: half of them gate rows,
+// half up rows, which lets the tiles of a short step cover more SMs).
+DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, int SK, float* ws,
+                         int bn, cudaStream_t st) {
+    if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr || SK < 1) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
-    if (mode == 2) return launch<256, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, st);
-    if (mode == 0) return launch<256, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, st);
+    const int k_blocks = (K + 63) / 64, k_per = (k_blocks + SK - 1) / SK;
+    if (SK > 1 && (mode != 0 || ws == nullptr || (SK - 1) * k_per >= k_blocks)) return (int)cudaErrorInvalidValue;
+    if (ws != nullptr && mode != 0) return (int)cudaErrorInvalidValue;
+    if (mode == 2 && bn == 128) return launch<128, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 2 && bn == 144) return launch<144, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 2 && bn == 160) return launch<160, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 2 && bn == 192) return launch<192, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 2) return launch<256, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 0 && bn == 128) return launch<128, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+    if (mode == 0) return launch<256, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
     return (int)cudaErrorInvalidValue;
 }

@@ -286,3 +286,4 @@ class GpuBackend:
             if s["slot"] is not None:
                 self.runner.end(s["slot"])
         self.seqs = None
+        api.gemm_tc_check()                   # the tensor-core kernels' bounded waits (decode steps of many rows)

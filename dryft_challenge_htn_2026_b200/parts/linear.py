@@ -47,6 +47,10 @@ def _linear(x, w, mode, allow_partial, residual):
         plan = api.stream_plan(M, N, K, mode, allow_partial or fuse)
         if plan is not None:
             return api.gemv_stream(x, w, None, mode, plan, residual if fuse else None)
+    if M <= api.TC_SKINNY_MAX_ROWS and K % 8 == 0:
+        # a decode step of 17 to 128 rows: weights streamed once by TMA, one 128-row tile of x,
+        # K in slices so that the few weight tiles still cover the SMs
+        return api.gemm_tc(x, w, mode, None, api.skinny_tc_plan(M, N, K, mode, allow_partial))
     if M <= api.GEMV_MAX_ROWS:
         return api.gemv_bf16(x, w, None, mode, api.gemv_plan(M, N, K, mode, allow_partial))
     if mode == STORE_F32:

@@ -515,3 +515,32 @@ def test_gemv_stream_applies_a_deferred_norm(M, N, K):
     if N % 2 == 0 and api.stream_plan(M, N // 2, K, api.MODE_SILU) is not None:
         g, u = (x.float() @ w.float().t()).chunk(2, dim=1)
         close(api.gemv_stream(lazy, w, None, api.MODE_SILU), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "deferred norm, silu")
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 6144, 2560), (33, 2560, 4096), (128, 2560, 9728), (17, 300, 520), (100, 1000, 1288)])
+def test_gemm_tc_on_a_decode_step_of_17_to_128_rows(M, N, K):
+    """One tile of rows, K in slices with float32 partial sums, weights requested before the wait
+    for the previous kernel (programmatic launch on, a kernel in front)."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, seed=81, scale=K ** -0.5)
+    ref = x.float() @ w.float().t()
+    api.set_pdl(True)
+    try:
+        plans = {api.skinny_tc_plan(M, N, K, api.MODE_STORE, True), (128, 1), (256, 1), (128, 2), (256, 3)}
+        for bn, sk in sorted(plans):
+            if sk > 1 and (sk - 1) * (((K + 63) // 64 + sk - 1) // sk) >= (K + 63) // 64:
+                continue
+            x2 = x.clone()                                               # a kernel in front of the product
+            r = api.gemm_tc(x2, w, api.MODE_STORE, None, (bn, sk))
+            assert isinstance(r, api.Partial) == (sk > 1)
+            close(r.sum() if sk > 1 else r, ref, torch.bfloat16, f"gemm_tc rows {M} plan {(bn, sk)}")
+        r = api.gemm_tc(x, w, api.MODE_STORE_F32)
+        assert r.dtype == torch.float32
+        close(r, ref, torch.bfloat16, "gemm_tc float32 out")
+        if N % 2 == 0:
+            g, u = ref.chunk(2, dim=1)
+            for bn in (128, 144, 160, 192, 256):
+                close(api.gemm_tc(x, w, api.MODE_SILU, None, (bn, 1)), g / (1 + torch.exp(-g)) * u, torch.bfloat16,
+                      f"gemm_tc silu, few rows, {bn} weight rows a tile")
+        api.gemm_tc_check()
+    finally:
+        api.set_pdl(False)
