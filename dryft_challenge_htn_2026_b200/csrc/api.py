@@ -211,9 +211,9 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=32, resident_blocks=3 * 148):
+def decode_splits(n_seq, n_kv_heads, group, max_splits=32, resident_blocks=2 * 148):
     """Number of key splits for decode attention: as many as keep all blocks resident at once
-    (three per SM), fixed for a batch size (it must not depend on sequence lengths, which change
+    (two per SM with the three-deep rings), fixed for a batch size (it must not depend on sequence lengths, which change
     under a captured graph)."""
     blocks = n_seq * n_kv_heads * ((group + 15) // 16)
     return max(1, min(max_splits, resident_blocks // blocks))
@@ -414,12 +414,13 @@ def tile_counters(device, n):
     return _counters[key]
 
 
-def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None):
+def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None, prefetch=None):
     """The weight-streaming skinny product (asynchronous copies into shared-memory rings,
     tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Same results and
     return convention as ``gemv_bf16``. ``x`` may be a ``Normed`` (the norm is applied while x is
     loaded; modes STORE and SILU). With ``residual`` (float32 [M, N], mode STORE) the product is
-    added into it in place and an ``Added`` is returned."""
+    added into it in place and an ``Added`` is returned. ``prefetch``: a contiguous tensor (the next
+    product's weights) that the kernel asks into L2 while it runs."""
     lazy = isinstance(x, Normed)
     if lazy:
         if x.dtype != torch.bfloat16 or mode == MODE_STORE_F32 or residual is not None:
@@ -461,7 +462,9 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None):
     _check(lib, lib.dk_gemv_stream(None if lazy else _p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, fuse,
                                    _p(x.h) if lazy else None, _p(x.sq) if lazy else None, x.sq.shape[0] if lazy else 0,
                                    _p(x.weight) if lazy else None, c_float(x.eps if lazy else 0.0), _p(residual), _p(sq),
-                                   _p(counters), _stream()), "gemv_stream")
+                                   _p(counters), _p(prefetch),
+                                   c_longlong(0 if prefetch is None else prefetch.numel() * prefetch.element_size()),
+                                   _stream()), "gemv_stream")
     if residual is not None:
         return Added(residual, sq)
     return Partial(ws) if sk > 1 else out

@@ -5,10 +5,10 @@
 //  * prefill: ragged batch of query chunks; a block owns 64 consecutive queries of one sequence
 //    and one query head (4 warps x 16 rows) and walks the key pages up to its diagonal.
 //  * decode: one query token per sequence; a block owns the (up to 16) query heads that share a
-//    kv head and one split of the keys; its 4 warps take 16 keys each of every 64-key page and
-//    are merged through shared memory; splits are merged by the combine kernel.
-// Key/value pages ([64, HD] per kv head, contiguous) are staged in shared memory with cp.async,
-// two stages deep. P is rounded to bfloat16 before P.V; row sums use the unrounded values.
+//    kv head and one split of the keys; its 4 warps take 16 keys each of every 64-key page, each
+//    through a cp.async ring of its own (2 or 3 chunks deep), and are merged through shared memory;
+//    splits are merged by the combine kernel.
+// Prefill stages key/value pages ([64, HD] per kv head, contiguous) with cp.async, two stages deep. P is rounded to bfloat16 before P.V; row sums use the unrounded values.
 // Reference formulas: engine/fused.py:301-343 (prefill), :478-565 (split decode + combine).
 #include "common.cuh"
 
@@ -233,6 +233,7 @@ attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v
 // sequence b's one query token (its key is already cached); < 0 marks a padding row.
 // nsplit == 1: writes out directly. Otherwise writes float32 partials
 // ws_acc [(b*nh + head)*nsplit + split][HD] and ws_ml [...][2] = (max in log2 domain, row sum).
+template <int D>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
                    const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
@@ -246,51 +247,64 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
     const int b = blockIdx.z;
     const int head0 = kvh * G + mt * 16;
     const int heads_here = min(16, G - mt * 16);
+    // Every warp streams its own 16 keys of each page (rows 16w..16w+15 of K and of V) through a
+    // ring of D chunks of its own: no block barrier until the warps' results are merged.
     // Positions and page tables are not written by the kernel before this one, and of the cache
-    // only the page of the newest token is (its key and value were just stored): the first page of
-    // this block, unless it is that one, is requested before the wait for that kernel.
+    // only the page of the newest token is (its key and value were just stored): chunks of older
+    // pages are requested before the wait for that kernel.
+    constexpr int CHUNK = 2 * 16 * KSTR;      // elements: 16 keys then 16 values
+    constexpr int CPR = HD / 8;               // 16-byte pieces per row
+    bf16* ring = smem + warp * D * CHUNK;
     const int pos = row_pos[b];
     const int* pt = page_table + (size_t)b * pt_stride;
     const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
     const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
-    const int jt0 = t_lo + split * per, jt1 = min(t_hi + 1, jt0 + per);  // [jt0, jt1)
-    const bool any = pos >= 0 && jt0 < jt1;
-    const bool early = any && jt0 < t_hi;
-    if (early) {
-        stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
+    const int jt0 = t_lo + split * per, jt1 = pos >= 0 ? min(t_hi + 1, jt0 + per) : jt0;  // [jt0, jt1)
+    auto fetch = [&](int jt, int slot) {
+        const size_t off = kv_offset(pt[jt], nkv, kvh, warp * 16, HD);
+        bf16* dst = ring + slot * CHUNK;
+        for (int c = lane; c < 16 * CPR; c += 32) {
+            const int row = c / CPR, col = (c % CPR) * 8;
+            cp_async16(dst + row * KSTR + col, k_store + off + (size_t)row * HD + col);
+            cp_async16(dst + 16 * KSTR + row * KSTR + col, v_store + off + (size_t)row * HD + col);
+        }
+    };
+    int issued = 0;                           // chunks requested so far; chunk i is commit group i
+    for (; issued < D && jt0 + issued < min(jt1, t_hi); issued++) {
+        fetch(jt0 + issued, issued);
         cp_async_commit();
     }
     pdl_wait();
     pdl_launch_dependents();
+    for (; issued < D; issued++) {            // the rest of the ring (the newest page, or nothing)
+        if (jt0 + issued < jt1) fetch(jt0 + issued, issued);
+        cp_async_commit();
+    }
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float acc[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-    if (any) {
+    if (jt0 < jt1) {
         uint32_t qf[HD / 16][4];
         const bf16* qb = q + ((size_t)b * nh + head0) * HD;
         load_q_frags(qf, g < heads_here ? qb + (size_t)g * HD : nullptr,
                      g + 8 < heads_here ? qb + (size_t)(g + 8) * HD : nullptr);
         const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
-        if (!early) {
-            stage_page(smem, k_store, v_store, pt[jt0], nkv, kvh);
-            cp_async_commit();
-        }
         for (int jt = jt0; jt < jt1; jt++) {
-            const int cur = (jt - jt0) & 1;
-            if (jt + 1 < jt1) stage_page(smem + (cur ^ 1) * STAGE_ELEMS, k_store, v_store, pt[jt + 1], nkv, kvh);
-            cp_async_commit();
-            cp_async_wait<1>();
-            __syncthreads();
+            const int slot = (jt - jt0) % D;
+            cp_async_wait<D - 1>();           // this warp's chunk jt has landed
+            __syncwarp();
             const int key0 = jt * DK_PAGE + warp * 16;
             if (key0 <= pos && key0 + 15 >= key_lo) {
-                const bf16* Ks = smem + cur * STAGE_ELEMS + warp * 16 * KSTR;
-                warp_attend<16>(qf, Ks, Ks + TILE_ELEMS, key0, lo, hi, sl2, m, l, acc);
+                const bf16* Ks = ring + slot * CHUNK;
+                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc);
             }
-            __syncthreads();
+            __syncwarp();                     // every lane is done reading the slot before it is refilled
+            if (jt + D < jt1) fetch(jt + D, slot);
+            cp_async_commit();
         }
     }
     cp_async_wait<0>();
@@ -440,12 +454,16 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int nspl
     }
 }
 
+constexpr size_t decode_smem(int depth) { return (size_t)4 * depth * 2 * 16 * KSTR * sizeof(bf16); }
+
 static int ensure_smem_attr() {
     static bool done = false;
     if (done) return 0;
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        e = cudaFuncSetAttribute(attn_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(attn_decode_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
     if (e != cudaSuccess) return (int)e;
     done = true;
     return 0;
@@ -475,9 +493,19 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
-    e = dk_launch(attn_decode_kernel, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), SMEM_BYTES, st, (const bf16*)q,
-                  (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
-                  nh, nkv, window, scale * 1.4426950408889634f, counters);
+    // ring depth: three chunks a warp while all blocks fit two to an SM, else two (three to an SM)
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long blocks = (long long)nsplit * nkv * mtiles * n_seq;
+    if (blocks <= 2LL * sms && 2 * (decode_smem(3) + 1024) <= 227 * 1024)
+        e = dk_launch(attn_decode_kernel<3>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(3), st, (const bf16*)q,
+                      (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
+                      nh, nkv, window, scale * 1.4426950408889634f, counters);
+    else
+        e = dk_launch(attn_decode_kernel<2>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(2), st, (const bf16*)q,
+                      (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
+                      nh, nkv, window, scale * 1.4426950408889634f, counters);
     if (e || nsplit == 1 || counters != nullptr) return e;   // (callers give counters only for nsplit <= 32)
     return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, nsplit, n_seq * nh);

@@ -100,6 +100,8 @@ struct Fuse {
     float* h_out;         // FUSE 2: residual stream [M,N], += product
     float* sq_out;        //         [tiles][16]
     int* counters;        //         [tiles], zero before and after every launch
+    const char* pf;       // a hint: [pf, pf + pf_bytes) (the next product's weights) is asked into L2
+    size_t pf_bytes;
 };
 
 // MR: rows of x kept (8 or 16, M <= MR). MODE as in gemm.cu. Mode 2: a tile's rows 0-7 are the
@@ -151,6 +153,17 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
     for (int d = 0; d < DEPTH; d++, head += WARPS) {
         if (head < total) fetch(head, d);
         cp_async_commit();
+    }
+    // The next product's weights: asked into L2 now, so that HBM keeps streaming through the short
+    // kernels that follow and that product starts on warm lines. Pieces are dealt round-robin.
+    if (fu.pf_bytes) {
+        constexpr size_t PIECE = 16384;
+        const size_t n = (fu.pf_bytes + PIECE - 1) / PIECE;
+        for (size_t i = (size_t)tid * gridDim.x + blockIdx.x; i < n; i += (size_t)gridDim.x * WARPS * 32) {
+            const size_t off = i * PIECE;
+            const unsigned sz = (unsigned)(fu.pf_bytes - off < PIECE ? (fu.pf_bytes - off) & ~(size_t)15 : PIECE);
+            if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(fu.pf + off), "r"(sz) : "memory");
+        }
     }
     GS_NOTE(0);
     pdl_wait();
@@ -384,9 +397,11 @@ int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int
 // squares sq_in [sq_tiles][16] of its rows, norm_w [K] and eps. fuse 2 (mode 0): the product is
 // added into h_out [M,N] float32, sq_out [ceil(N/16)][16] gets the new rows' sums of squares per
 // 16 columns; counters: ceil(N/16) ints, zero (the kernel leaves them zero); ws needed if SK > 1.
+// pf, pf_bytes: memory (16-byte aligned) to ask into L2 while this product runs, or null / 0.
 DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws, int M, int N, int K, int mode, int SK,
                              int blocks, int fuse, const float* h_in, const float* sq_in, int sq_tiles, const float* norm_w,
-                             float eps, float* h_out, float* sq_out, int* counters, cudaStream_t st) {
+                             float eps, float* h_out, float* sq_out, int* counters, const void* pf, long long pf_bytes,
+                             cudaStream_t st) {
     if (M < 1 || M > 16 || K % 16 != 0 || SK < 1 || blocks < SK || slice_len(K, SK) > XMAX) return (int)cudaErrorInvalidValue;
     if (SK > 1 && (mode == 2 || ws == nullptr)) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)W) % 16 != 0) return (int)cudaErrorInvalidValue;
@@ -396,7 +411,8 @@ DK_EXPORT int dk_gemv_stream(const void* x, const void* W, void* out, float* ws,
     if (fuse == 0 && !x) return (int)cudaErrorInvalidValue;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    Fuse fu{h_in, sq_in, norm_w, eps, sq_tiles, h_out, sq_out, counters};
+    if (pf_bytes < 0 || (pf_bytes > 0 && (pf == nullptr || (uintptr_t)pf % 16 != 0))) return (int)cudaErrorInvalidValue;
+    Fuse fu{h_in, sq_in, norm_w, eps, sq_tiles, h_out, sq_out, counters, (const char*)pf, (size_t)pf_bytes};
 #define GS_CASE(MR)                                                                                      \
     if (fuse == 1 && mode == 0) return launch<MR, 0, 1>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);   \
     if (fuse == 1) return launch<MR, 2, 1>(xp, wp, out, ws, M, N, K, SK, blocks, fu, st);                \

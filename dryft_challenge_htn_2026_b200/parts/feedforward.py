@@ -32,7 +32,7 @@ class GatedMLP(Part):
         return [self.w_gate_up, self.w_down]
 
     def forward(self, ctx, a, residual=None):
-        return linear(linear(a, self.w_gate_up, SILU, ctx, gap_follows=False), self.w_down, ctx=ctx, allow_partial=True,
+        return linear(linear(a, self.w_gate_up, SILU, ctx), self.w_down, ctx=ctx, allow_partial=True,
                       residual=residual)
 
 

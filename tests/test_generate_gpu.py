@@ -139,10 +139,10 @@ def test_products_that_add_into_the_residual_and_apply_the_deferred_norm(tmp_pat
     seen = {"residual": 0, "deferred": 0}
     inner = api.gemv_stream
 
-    def counting(x, w, out=None, mode=api.MODE_STORE, plan=None, residual=None):
+    def counting(x, w, out=None, mode=api.MODE_STORE, plan=None, residual=None, prefetch=None):
         seen["residual"] += residual is not None
         seen["deferred"] += isinstance(x, api.Normed)
-        return inner(x, w, out, mode, plan, residual)
+        return inner(x, w, out, mode, plan, residual, prefetch)
 
     monkeypatch.setattr(api, "gemv_stream", counting)
     steps = list(dk.Engine(folder, dtype=torch.bfloat16, use_graph=False).generate(prompts, 16))
