@@ -219,6 +219,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -245,6 +246,12 @@ def main():
     model = dk.random_model(cfg, seed=0, dtype=torch.bfloat16)
     pk = peaks()
 
+    if args.prefill_only:
+        ms, flops = time_prefill(torch, dk, model, PROMPT)
+        print(json.dumps({"prefill": {"value": round(PROMPT / ms * 1e3, 1), "tokens": PROMPT, "ms": round(ms, 3),
+                                      "layers": cfg.num_hidden_layers,
+                                      "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
+        return 0
     main_run = time_decode(torch, dk, model, args.batch, args.steps, warmup, seed=0)
     e2e_val, h2d, d2h = time_e2e(torch, dk, model, args.batch, args.steps, seed=0)
     points, prefill = {}, None
