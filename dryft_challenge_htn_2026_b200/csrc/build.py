@@ -45,6 +45,21 @@ def _say(msg):
     print(f"[dryft-b200] {msg}", file=sys.stderr, flush=True)
 
 
+def build_dir():
+    """``csrc/_build`` in the tree; if the tree cannot be written (another user's checkout), a
+    folder of this user's under the temporary directory."""
+    try:
+        os.makedirs(BUILD_DIR, exist_ok=True)
+        if os.access(BUILD_DIR, os.W_OK):
+            return BUILD_DIR
+    except OSError:
+        pass
+    import tempfile
+    alt = os.path.join(tempfile.gettempdir(), f"dryft_b200_build_{os.getuid()}")
+    os.makedirs(alt, exist_ok=True)
+    return alt
+
+
 def lib_path(source, defines=None):
     defines = dict(defines or {})
     with open(os.path.join(HERE, source), "rb") as f:
@@ -55,7 +70,9 @@ def lib_path(source, defines=None):
     tag = "_".join(f"{k}{v}" for k, v in sorted(defines.items()))
     h = hashlib.sha1(text + repr((ARCH_FLAGS, NVCC_FLAGS, sorted(defines.items()))).encode()).hexdigest()[:12]
     stem = os.path.splitext(source)[0]
-    return os.path.join(BUILD_DIR, f"{stem}{'_' + tag if tag else ''}_{h}.so")
+    name = f"{stem}{'_' + tag if tag else ''}_{h}.so"
+    in_tree = os.path.join(BUILD_DIR, name)
+    return in_tree if os.path.exists(in_tree) else os.path.join(build_dir(), name)
 
 
 def compile_lib(source, defines=None, verbose=False):
@@ -63,7 +80,6 @@ def compile_lib(source, defines=None, verbose=False):
     out = lib_path(source, defines)
     if os.path.exists(out):
         return out
-    os.makedirs(BUILD_DIR, exist_ok=True)
     tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
     cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *(f"-D{k}={v}" for k, v in sorted((defines or {}).items())),
            *(["-Xptxas", "-v"] if verbose else []), "-I", HERE, "-o", tmp, os.path.join(HERE, source)]
