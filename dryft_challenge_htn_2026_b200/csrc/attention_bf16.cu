@@ -156,7 +156,7 @@ __device__ __forceinline__ void warp_attend(const uint32_t (&qf)[HD / 16][4], co
 }
 
 // ------------------------------------------------------------------------------------- prefill
-// grid (tiles, nh). tiles[2i] = sequence, tiles[2i+1] = first query of the tile within the
+// grid (nh, tiles). tiles[2i] = sequence, tiles[2i+1] = first query of the tile within the
 // sequence's chunk. cu_q: first flat row of each sequence's chunk; seq_pos0: tokens already cached
 // before the chunk (the chunk's own keys are in the cache when this runs).
 __global__ void __launch_bounds__(128)
@@ -167,8 +167,10 @@ attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    // heads vary fastest: blocks start in launch order, so every head's heaviest tile (the tiles
+    // are sorted by the keys they see) starts before any light one, and the light ones fill the end
+    const int seq = tiles[2 * blockIdx.y], q0 = tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x, kvh = h / (nh / nkv);
     const int q_len = cu_q[seq + 1] - cu_q[seq];
     const int pos0 = seq_pos0[seq];
     const int rows_here = min(64, q_len - q0);
@@ -477,7 +479,7 @@ DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store
     if (nh % nkv != 0) return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
-    return dk_launch(attn_prefill_kernel, dim3(n_tiles, nh), dim3(128), SMEM_BYTES, st, (const bf16*)q, (bf16*)out,
+    return dk_launch(attn_prefill_kernel, dim3(nh, n_tiles), dim3(128), SMEM_BYTES, st, (const bf16*)q, (bf16*)out,
                      (const bf16*)k_store, (const bf16*)v_store, tiles, cu_q, seq_pos0, page_table, pt_stride, nh, nkv,
                      window, scale * 1.4426950408889634f);
 }

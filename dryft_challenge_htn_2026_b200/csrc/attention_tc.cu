@@ -139,7 +139,7 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// grid (tiles, nh), 320 threads. tiles[2i] = sequence, tiles[2i+1] = first query (of 128) within
+// grid (nh, tiles), 320 threads. tiles[2i] = sequence, tiles[2i+1] = first query (of 128) within
 // the sequence's chunk. q / out [T, nh*HD]; map_q over q as [T, nh*HD]; map_k / map_v over one
 // layer's K / V store as [pages * nkv * 64, HD].
 // Threads 0..255: softmax, two threads per query row (thread t and t+128 share row t & 127 and
@@ -160,8 +160,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
-    const int seq = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
-    const int h = blockIdx.y, kvh = h / (nh / nkv);
+    // heads vary fastest: blocks start in launch order, so every head's heaviest tile (the tiles
+    // are sorted by the keys they see) starts before any light one, and the light ones fill the end
+    const int seq = tiles[2 * blockIdx.y], q0 = tiles[2 * blockIdx.y + 1];
+    const int h = blockIdx.x, kvh = h / (nh / nkv);
     const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
     const int rows_here = min(BM, q_len - q0);
     const int flat0 = cu_q[seq] + q0;                      // first flat row of this tile
@@ -426,6 +428,6 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
     if (!e) e = make_map(&mk, k_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
     if (!e) e = make_map(&mv, v_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
     if (e) return e;
-    return dk_launch(attn_prefill_tc_kernel, dim3(n_tiles, nh), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, cu_q,
+    return dk_launch(attn_prefill_tc_kernel, dim3(nh, n_tiles), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, cu_q,
                      seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err);
 }
