@@ -33,6 +33,9 @@ class GQAAttention(Part):
         self.q_norm = build_part(s.qk_norm, rt) if s.qk_norm is not None else None
         self.k_norm = build_part(s.qk_norm, rt) if s.qk_norm is not None else None
         self.position = build_part(s.position, rt) if s.position is not None else None
+        if self.position is not None and not getattr(self.position, "fused_tables", False) and s.qk_norm is not None:
+            raise ValueError("a position encoding that rewrites q and k itself (no fused tables) runs before the "
+                             "per-head q/k norm; with qk_norm set that is not the order of this mixer")
         self.max_positions = 0
         # decode in one launch (norm + rotation + cache write + attention + merge) instead of three;
         # measured a few percent slower inside the full step on B200, so it is off by default

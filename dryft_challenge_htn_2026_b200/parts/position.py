@@ -2,9 +2,12 @@
 
 The part owns the angle tables; the rotation itself is fused into the kernel that also
 normalises q/k heads and writes the cache, which takes the tables as arguments. Another position
-encoding is another part with the same two methods: ``tables(n)`` if the fused kernel can use it,
-or ``apply(q, k, ctx)`` for one that rewrites q and k itself (the attention part then runs the
-fused kernel without rotation)."""
+encoding is another part: with ``fused_tables = True`` and ``tables(n)`` (cos, sin [n, dim/2]
+float32) if the fused kernel can use it, or with ``apply(qkv, ctx, n_heads, n_kv_heads, head_dim)``
+for one that rewrites the q and k heads of the projection rows [tokens, (nh + 2 nkv) * hd] in place
+itself; the attention part then runs the fused kernel without rotation. ``apply`` runs before the
+cache write and cannot be combined with a per-head q/k norm (which would have to come first): the
+attention part refuses that pair."""
 import torch
 
 from ..config.specs import RotaryHalfSpec
