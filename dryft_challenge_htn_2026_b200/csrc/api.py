@@ -211,12 +211,16 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=32, resident_blocks=2 * 148):
-    """Number of key splits for decode attention: as many as keep all blocks resident at once
-    (two per SM with the three-deep rings), fixed for a batch size (it must not depend on sequence lengths, which change
-    under a captured graph)."""
+def decode_splits(n_seq, n_kv_heads, group, max_splits=16, resident_blocks=2 * 148):
+    """Number of key splits for decode attention, fixed for a batch size (it must not depend on
+    sequence lengths, which change under a captured graph). While all blocks fit the GPU at once
+    (two per SM with the three-deep rings): as many splits as keep it so. Beyond that: enough for
+    about six waves of blocks, which evens out sequences of unequal lengths (measured at batch 64:
+    133 us unsplit, 115 us in four splits)."""
     blocks = n_seq * n_kv_heads * ((group + 15) // 16)
-    return max(1, min(max_splits, resident_blocks // blocks))
+    if blocks <= resident_blocks:
+        return max(1, min(max_splits, resident_blocks // blocks))
+    return max(1, min(max_splits, -(-6 * resident_blocks // blocks)))
 
 
 def attention_decode_ws(n_seq, n_heads, head_dim, nsplit, device):
