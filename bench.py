@@ -263,7 +263,7 @@ def main():
                    "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     out = {
-        "metric": "decode tok/s at batch 8 (Qwen3-4B, bf16)", "value": round(main_run["tok_s"], 1), "unit": "tok/s",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-4B, bf16)", "value": round(main_run["tok_s"], 1), "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids",
