@@ -214,7 +214,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=48,
+                    help="untimed steps before the timed ones; the default outlasts the tens of milliseconds the SM clock "
+                         "takes to come back after the power-capped prefill")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

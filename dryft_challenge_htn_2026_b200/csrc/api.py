@@ -356,6 +356,9 @@ def l2_prefetch(t, stream=None):
 
 # ------------------------------------------------------------------- streaming product (M <= 16)
 STREAM_MAX_ROWS = 16
+# rows up to which the streaming product is the fastest: with 9 to 16 rows its copy of x doubles and
+# only one block fits an SM, and the tensor-core product in its decode form wins (measured at 12, 16, 17)
+STREAM_BEST_ROWS = 8
 STREAM_BUILD = None   # compile-time overrides of the kernel's stage size, ring depth and warp count (tuning)
 
 def stream_plan(M, N, K, mode, allow_partial=False):

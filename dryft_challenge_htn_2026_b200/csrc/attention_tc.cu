@@ -288,7 +288,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // the row's maximum is over both threads of the row
             xch[(i & 1) * 256 + threadIdx.x] = mx;
             if (threadIdx.x == 0) TRACE(7);
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
             if (threadIdx.x == 0) TRACE(3);
             float m_new = fmaxf(m, fmaxf(mx, xch[(i & 1) * 256 + (threadIdx.x ^ 128)]));
             // a maximum that moved by less than 8 (a factor 256) keeps the old reference: P stays well inside
@@ -339,7 +339,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok && n_blk > 0) ok = mbar_wait(bar_o, (n_blk - 1) & 1);
         // the row's sum is over both threads of the row
         xch[threadIdx.x] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
         l += xch[threadIdx.x ^ 128];
         if (ok) {
             fence_after();

@@ -92,7 +92,7 @@ class CausalLM:
     def forward(self, ctx, cache):
         s, rt = self.spec, self.rt
         ctx.prefetcher = None
-        if self.prefetch and ctx.is_decode and rt.dtype == torch.bfloat16 and ctx.n_tok <= api.STREAM_MAX_ROWS:
+        if self.prefetch and ctx.is_decode and rt.dtype == torch.bfloat16 and ctx.n_tok <= api.STREAM_BEST_ROWS:
             if self._prefetcher is None:
                 from .prefetch import WeightPrefetcher
                 self._prefetcher = WeightPrefetcher(self.weights_in_order())

@@ -1,10 +1,11 @@
 """out = x . W^T for a weight [out, in] without bias: picks the kernel by dtype and row count.
 
-float32: the CUDA-core sgemm for every size (a true 32-bit product). bfloat16: the streaming
-kernels that read the weights once for up to 64 rows (decode); for more rows (prefill) the
-TMA + tcgen05 kernel, always for the gated product (SiLU*up fused into its epilogue) and otherwise
-when its 128 x 256 tiles fill the GPU's waves, else the library matrix product (the reference uses
-the library for all of these, engine/fused.py:993-995)."""
+float32: the CUDA-core sgemm for every size (a true 32-bit product). bfloat16: up to 8 rows the
+streaming kernel (cp.async rings, weights read once); up to 128 rows the TMA + tcgen05 kernel in its
+decode form (one tile of rows, K in slices); for more rows (prefill) the same kernel, always for the
+gated product (SiLU*up fused into its epilogue) and otherwise when its 128 x 256 tiles fill the
+GPU's waves, else the library matrix product (the reference uses the library for all of these,
+engine/fused.py:993-995)."""
 import torch
 
 from ..csrc import api
@@ -30,7 +31,7 @@ def _linear(x, w, mode, allow_partial, residual, prefetch):
     M, K = x.shape
     N = w.shape[0] // 2 if mode == SILU else w.shape[0]
     if isinstance(x, api.Normed):
-        if x.dtype == torch.bfloat16 and M <= api.STREAM_MAX_ROWS and K % 16 == 0 and mode != STORE_F32:
+        if x.dtype == torch.bfloat16 and M <= api.STREAM_BEST_ROWS and K % 16 == 0 and mode != STORE_F32:
             plan = api.stream_plan(M, N, K, mode, allow_partial)
             if plan is not None:
                 return api.gemv_stream(x, w, None, mode, plan, prefetch=prefetch)
@@ -39,7 +40,7 @@ def _linear(x, w, mode, allow_partial, residual, prefetch):
         out = torch.empty((M, N), dtype=torch.float32, device=x.device)
         api.sgemm(x, w, out, mode)
         return out
-    if M <= api.STREAM_MAX_ROWS and K % 16 == 0:
+    if M <= (api.STREAM_BEST_ROWS if K % 8 == 0 else api.STREAM_MAX_ROWS) and K % 16 == 0:
         fuse = residual is not None and mode == STORE
         plan = api.stream_plan(M, N, K, mode, allow_partial or fuse)
         if plan is not None:
