@@ -9,8 +9,8 @@
 // from a gate tile and an up tile side by side in one 256-column accumulator); two accumulators
 // alternate in tensor memory so the epilogue of a tile overlaps the mma of the next.
 //   warp 0   producer: one thread issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte
-//            swizzle) of x [128 x 64] and W [BN x 64] into a 4-stage shared-memory ring; an
-//            mbarrier per stage counts the bytes.
+//            swizzle) of x [128 x 64] and W [BN x 64] into a shared-memory ring of 4 stages (up
+//            to 12 when few rows of x are loaded); an mbarrier per stage counts the bytes.
 //   warp 1   allocates BN columns of tensor memory; one thread issues tcgen05.mma
 //            (cta_group::1, kind::f16, M = 128, N = BN, K = 16, four per stage) from shared-memory
 //            matrix descriptors, and tcgen05.commit hands each stage back / signals the epilogue.
@@ -32,9 +32,8 @@
 namespace {
 
 constexpr int BM = 128, BK = 64;
-// stages of the load ring for BN weight rows a tile: as many as fit in about 200 KB, at most 8
-__host__ __device__ constexpr int stages_for(int bn) { return (200 * 1024) / (BM * BK * 2 + bn * BK * 2) > 8 ? 8 : (200 * 1024) / (BM * BK * 2 + bn * BK * 2); }
-constexpr int A_BYTES = BM * BK * 2;
+constexpr int A_BYTES = BM * BK * 2;     // what the mma reads of x per stage: 128 rows of 128 bytes
+constexpr int MAX_STAGES = 12;
 constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,16 +97,21 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 template <int BN, int MODE>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, bf16* out, int M,
-               int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws) {
+               int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws, int STAGES, int a_bytes) {
     constexpr int B_BYTES = BN * BK * 2;
-    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int STAGES = stages_for(BN);
+    // Shared memory: STAGES weight tiles, then STAGES tiles of x a_bytes apart, then the barriers.
+    // a_bytes = rows of x that are really loaded x 128 bytes. The mma always reads 128 rows (A_BYTES)
+    // from a tile's start: with fewer loaded rows (a decode step) it reads on into the next tiles or
+    // the padding behind the last one. Those rows of the accumulator are garbage and never stored;
+    // what they cost is nothing, what they save is shared memory for more weight tiles in flight.
     constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators; allocations are powers of two
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;   // outputs per tile
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // the swizzle pattern repeats every 1024 bytes
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint8_t* smem_a = smem + STAGES * B_BYTES;
+    const uint32_t stage_tx = (uint32_t)(B_BYTES + a_bytes);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_a + (STAGES - 1) * a_bytes + A_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;     // [2] mma -> epilogue
     uint64_t* acc_empty = acc_full + 2;      // [2] epilogue -> mma
@@ -144,39 +148,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (warp == 0) {
         if (lane == 0) {  // ------------------------------------------------------------ producer
             int it = 0;   // stages issued so far, over all units of this block
+            int s = 0;    // it % STAGES, and round = (it / STAGES) & 1, kept by counting (no division on this path)
+            uint32_t round = 0;
             bool waited = !early_w;
-            int early_kb[STAGES], early_m0[STAGES];   // stages whose rows of x are still to be requested
+            int early_kb[MAX_STAGES], early_m0[MAX_STAGES];   // stages whose rows of x are still to be requested
             auto flush = [&](int n) {                 // the previous kernel's output may be read from here on
                 pdl_wait();
                 pdl_launch_dependents();
                 waited = true;
-                for (int j = 0; j < n; j++) tma_load_2d(smem + j * STAGE_BYTES, &map_x, early_kb[j] * BK, early_m0[j], &full[j]);
+                for (int j = 0; j < n; j++) tma_load_2d(smem_a + j * a_bytes, &map_x, early_kb[j] * BK, early_m0[j], &full[j]);
             };
             for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
                 const int tile = unit / SK, slice = unit % SK;
                 const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
                 const int kb0 = slice * k_per, kb1 = min(k_blocks, kb0 + k_per);
-                for (int kb = kb0; kb < kb1; kb++, it++) {
-                    const int s = it % STAGES;
+                for (int kb = kb0; kb < kb1; kb++, it++, s = s + 1 == STAGES ? 0 : s + 1, round ^= (s == 0)) {
                     if (!waited && it == STAGES) flush(STAGES);   // the ring is full of weights
-                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1)) {
+                    if (it >= STAGES && !mbar_wait(&empty[s], round ^ 1)) {
                         atomicExch(err, 1);
                         unit = units;
                         break;
                     }
-                    uint8_t* stage = smem + s * STAGE_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    uint8_t* stage = smem + s * B_BYTES;
+                    mbar_expect_tx(&full[s], stage_tx);
                     if (waited) {
-                        tma_load_2d(stage, &map_x, kb * BK, m0, &full[s]);
+                        tma_load_2d(smem_a + s * a_bytes, &map_x, kb * BK, m0, &full[s]);
                     } else {
                         early_kb[it] = kb;
                         early_m0[it] = m0;
                     }
                     if (MODE == 2) {
-                        tma_load_2d(stage + A_BYTES, &map_w, kb * BK, n0, &full[s]);
-                        tma_load_2d(stage + A_BYTES + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
+                        tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
+                        tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
                     } else {
-                        tma_load_2d(stage + A_BYTES, &map_w, kb * BK, n0, &full[s]);
+                        tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
                     }
                 }
             }
@@ -184,7 +189,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
     } else if (warp == 1) {
         if (lane == 0) {  // ---------------------------------------------------------- mma issuer
-            int it = 0, iter = 0;
+            int iter = 0, s = 0;
+            uint32_t round = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, iter++) {
                 const int slice = unit % SK;
@@ -197,15 +203,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem + buf * BN;
-                for (int kb = kb0; kb < kb1; kb++, it++) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) {
+                for (int kb = kb0; kb < kb1; kb++, s = s + 1 == STAGES ? 0 : s + 1, round ^= (s == 0)) {
+                    if (!mbar_wait(&full[s], round)) {
                         atomicExch(err, 2);
                         ok = false;
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                    const uint32_t a_addr = smem_u32(smem_a + s * a_bytes), b_addr = smem_u32(smem + s * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)
                         umma_f16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb > kb0) | (k != 0));
@@ -318,16 +323,23 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 template <int BN, int MODE>
 int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, int SK, float* ws, cudaStream_t st) {
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;
-    constexpr int STAGES = stages_for(BN);
-    constexpr size_t smem = 1024 + (size_t)STAGES * (A_BYTES + BN * BK * 2) + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
-    static bool attr = false;
-    if (!attr) {
+    constexpr int B_BYTES = BN * BK * 2;
+    // rows of x a TMA box loads: all 128 of a tile, or for a single tile of few rows (a decode step)
+    // the next of 16, 32, 64 that holds them, which leaves shared memory for more weight tiles in flight
+    const int a_rows = M > 64 ? 128 : M > 32 ? 64 : M > 16 ? 32 : 16;
+    const int a_bytes = a_rows * BK * 2;
+    int stages = (200 * 1024 - (A_BYTES - a_bytes)) / (B_BYTES + a_bytes);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    const size_t smem = 1024 + (size_t)stages * B_BYTES + (size_t)(stages - 1) * a_bytes + A_BYTES +
+                        (2 * MAX_STAGES + 4) * sizeof(uint64_t) + 16;
+    static size_t attr = 0;
+    if (smem > attr) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        attr = true;
+        attr = smem;
     }
     CUtensorMap mx, mw;
-    int e = make_map(&mx, x, M, K, BM);
+    int e = make_map(&mx, x, M, K, a_rows);
     if (e) return e;
     e = make_map(&mw, W, MODE == 2 ? 2LL * N : N, K, MODE == 2 ? BN / 2 : BN);
     if (e) return e;
@@ -337,7 +349,7 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(units < sms ? units : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
-                     m_tiles, tiles, err, SK, ws);
+                     m_tiles, tiles, err, SK, ws, stages, a_bytes);
 }
 
 }  // namespace
