@@ -333,6 +333,58 @@ __global__ void add_rmsnorm_wide_kernel(float* h, const bf16* delta, const float
     }
 }
 
+// The same with one warp per row (H % 256 == 0, H <= 4096): every load of the row is requested
+// before any is used, the sum of squares needs shuffles only, and no block barrier is on the path.
+template <int CH>   // CH = H / 256 chunks of 8 elements per lane
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* h, const bf16* delta, const float* __restrict__ w, float eps, int n_rows, bf16* a) {
+    constexpr int H = CH * 256;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= (size_t)n_rows) return;
+    float4* hr = reinterpret_cast<float4*>(h + row * H);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * H) : nullptr;
+    float v[CH][8];
+    uint4 d8[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        const int i = c * 32 + lane;          // index of this lane's 8 elements
+        const float4 x0 = hr[2 * i], x1 = hr[2 * i + 1];
+        v[c][0] = x0.x, v[c][1] = x0.y, v[c][2] = x0.z, v[c][3] = x0.w;
+        v[c][4] = x1.x, v[c][5] = x1.y, v[c][6] = x1.z, v[c][7] = x1.w;
+        if (dr) d8[c] = dr[i];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        const int i = c * 32 + lane;
+        if (dr) {
+            float d[8];
+            unpack8(d8[c], d);
+#pragma unroll
+            for (int k = 0; k < 8; k++) v[c][k] += d[k];
+            hr[2 * i] = make_float4(v[c][0], v[c][1], v[c][2], v[c][3]);
+            hr[2 * i + 1] = make_float4(v[c][4], v[c][5], v[c][6], v[c][7]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; k++) ss += v[c][k] * v[c][k];
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    uint4* ar = reinterpret_cast<uint4*>(a + row * H);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+        const int i = c * 32 + lane;
+        const float4 w0 = wr[2 * i], w1 = wr[2 * i + 1];
+        float o[8] = {v[c][0] * rs * w0.x, v[c][1] * rs * w0.y, v[c][2] * rs * w0.z, v[c][3] * rs * w0.w,
+                      v[c][4] * rs * w1.x, v[c][5] * rs * w1.y, v[c][6] * rs * w1.z, v[c][7] * rs * w1.w};
+        ar[i] = pack8(o);
+    }
+}
+
 // q/k norm + rotation + cache write for bfloat16 with head sizes that are multiples of 16. A group
 // of GS lanes (GS = the power of two >= head_dim / 16) takes one (token, head); a warp takes 32 / GS
 // of them. Lane j of a group holds elements [8j, 8j+8) of each half of the head.
@@ -416,6 +468,15 @@ DK_EXPORT int dk_embed_rmsnorm(int dtype, const int* tok, const void* embed, con
 DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float* parts, int n_parts,
                              long long part_stride, const int* rows, const float* w, float eps, int n_rows, int H,
                              void* a, cudaStream_t st) {
+    if (dtype == 1 && parts == nullptr && rows == nullptr && H % 256 == 0 && H <= 4096 && n_rows > 64) {
+        const dim3 grid((n_rows + 7) / 8), block(256);
+#define NORM_WARP(CH)                                                                                                   \
+    if (H == CH * 256)                                                                                                  \
+        return dk_launch(add_rmsnorm_warp_kernel<CH>, grid, block, 0, st, h, (const bf16*)delta, w, eps, n_rows, (bf16*)a)
+        NORM_WARP(1); NORM_WARP(2); NORM_WARP(3); NORM_WARP(4); NORM_WARP(5); NORM_WARP(6); NORM_WARP(7); NORM_WARP(8);
+        NORM_WARP(9); NORM_WARP(10); NORM_WARP(11); NORM_WARP(12); NORM_WARP(13); NORM_WARP(14); NORM_WARP(15); NORM_WARP(16);
+#undef NORM_WARP
+    }
     if (dtype == 1 && parts == nullptr && rows == nullptr && H % 8 == 0 && H <= 8 * 4 * row_threads(H) && n_rows > 64)
         return dk_launch(add_rmsnorm_wide_kernel, dim3(n_rows), dim3(row_threads(H)), 0, st, h, (const bf16*)delta, w, eps,
                          H, (bf16*)a);

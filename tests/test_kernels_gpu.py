@@ -43,7 +43,7 @@ def test_embed_rmsnorm(dtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H", [(1, 64), (33, 2560), (70, 200)])
+@pytest.mark.parametrize("T,H", [(1, 64), (33, 2560), (70, 200), (130, 2560), (67, 512), (100, 4096)])
 def test_add_rmsnorm_and_row_gather(dtype, T, H):
     h0, delta, w = rnd(T, H, seed=3, scale=3.0), rnd(T, H, dtype=dtype, seed=4), 1 + 0.1 * rnd(H, seed=5)
     h = h0.clone()
