@@ -1,0 +1,49 @@
+"""Host-side launch planning (no GPU): how products are cut into slices and tiles, how many key
+splits decode attention gets. The kernels refuse plans that break these invariants; the planners
+must never produce one."""
+import itertools
+
+from dryft_challenge_htn_2026_b200.csrc import api
+
+
+def test_stream_plan_keeps_a_slice_of_x_in_shared_memory_and_splits_only_when_allowed():
+    for M, N, K in itertools.product((1, 8, 16), (72, 2560, 6144, 151936), (304, 2560, 4096, 9728, 20000)):
+        for mode, partial in ((api.MODE_STORE, False), (api.MODE_STORE, True), (api.MODE_STORE_F32, False), (api.MODE_SILU, False)):
+            plan = api.stream_plan(M, N, K, mode, partial)
+            if plan is None:                      # only when K needs slices that the caller or the epilogue cannot take
+                assert K > 2560 and (mode == api.MODE_SILU or not partial)
+                continue
+            sk, blocks = plan
+            assert sk >= 1 and blocks >= sk
+            assert ((K + sk - 1) // sk + 15) // 16 * 16 <= 2560
+            assert sk == 1 or (partial and mode != api.MODE_SILU)
+
+
+def test_skinny_tc_plan_gives_every_slice_work_and_no_more_units_than_sms():
+    for M, N, K in itertools.product((9, 16, 64, 128), (304, 2560, 6144, 9728, 151936), (64, 520, 2560, 4096, 9728)):
+        for mode, partial in ((api.MODE_STORE, True), (api.MODE_STORE, False), (api.MODE_SILU, False), (api.MODE_STORE_F32, False)):
+            bn, sk = api.skinny_tc_plan(M, N, K, mode, partial)
+            kb = (K + 63) // 64
+            assert bn in ((128, 144, 160, 192, 256) if mode == api.MODE_SILU else (128, 256))
+            assert sk >= 1 and (sk - 1) * ((kb + sk - 1) // sk) < kb          # no slice without a block of K
+            assert sk == 1 or (mode == api.MODE_STORE and partial)
+            if sk > 1:
+                assert ((N + bn - 1) // bn) * sk <= api.SM_COUNT
+    # the gated product of the benchmark model: the tile width that covers most SMs in one wave
+    assert api.skinny_tc_plan(64, 9728, 2560, api.MODE_SILU) == (144, 1)
+
+
+def test_decode_splits_depend_on_the_batch_only_and_stay_within_what_the_merge_takes():
+    seen = {}
+    for n_seq, nkv, group in itertools.product((1, 2, 8, 16, 32, 64, 128, 500), (1, 2, 8), (1, 4, 16, 20)):
+        n = api.decode_splits(n_seq, nkv, group)
+        assert 1 <= n <= 32
+        seen[(n_seq, nkv, group)] = n
+    assert seen[(8, 8, 4)] == 4 and seen[(32, 8, 4)] == 1 and seen[(64, 8, 4)] == 4   # measured choices for the benchmark model
+    assert seen[(1, 8, 4)] == 16
+
+
+def test_gemm_tc_fills_gpu_is_about_the_last_wave():
+    assert api.gemm_tc_fills_gpu(2048, 19456 // 2)            # 16 x 38 tiles: 4.1 waves
+    assert not api.gemm_tc_fills_gpu(2048, 2560)              # 160 tiles on 148 SMs: a second wave of 12
+    assert api.gemm_tc_fills_gpu(128 * 148, 256)
