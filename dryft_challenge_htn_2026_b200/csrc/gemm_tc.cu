@@ -244,8 +244,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 if (MODE == 2) {
                     uint32_t u[32];
                     tmem_ld32(acc + OUT_COLS + c, u);
+                    // only rows that exist: the others hold zeros or whatever the mma read beyond the loaded rows,
+                    // and a division by the slow path (zero, infinite or NaN operands) for 100 idle rows of a decode
+                    // step made this epilogue 10 us longer
+                    if (row < M) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+                        for (int i = 0; i < 32; i++) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+                    }
                 }
                 if (row < M && ws != nullptr) {   // float32 partial sums of this slice
                     float* dst = ws + ((size_t)slice * M + row) * N + n0 + c;
