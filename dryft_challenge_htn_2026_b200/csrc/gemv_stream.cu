@@ -52,8 +52,14 @@ namespace {
 
 constexpr int STAGE_K = 256;                  // elements of K per stage
 constexpr int ROW_STRIDE = STAGE_K * 2 + 16;  // bytes between rows of a stage: 16 of padding keep ldmatrix conflict-free
-constexpr int DEPTH = 2;                      // stages a warp has in flight
-constexpr int WARPS = 4;
+#ifndef GS_DEPTH
+#define GS_DEPTH 2
+#endif
+#ifndef GS_WARPS
+#define GS_WARPS 4
+#endif
+constexpr int DEPTH = GS_DEPTH;               // stages a warp has in flight
+constexpr int WARPS = GS_WARPS;
 constexpr int WR = 16;                        // weight rows per stage
 constexpr int STAGE_BYTES = WR * ROW_STRIDE;
 constexpr int XMAX = 2560;                    // longest slice of K whose x rows are kept in shared memory
