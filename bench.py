@@ -103,11 +103,7 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
     rs = np.random.RandomState(seed + 1)
     prompts = [rs.randint(0, model.spec.vocab_size, n).tolist() for n in lens]
     params = SamplingParams(total_new)
-    # prompts go in a few sequences at a time to bound the activations of the prefill
-    backend_prompts = prompts
-    pending = backend.start(backend_prompts, params, [0] * batch) if batch <= 8 else start_in_pieces(
-        torch, backend, runner, prompts, params)
-    pending.wait()
+    backend.start(prompts, params, [0] * batch).wait()     # prefill (in steps of at most 32k tokens) and the first token
     st = backend.state
     count0 = api.launch_count()
     st.body(advance=False, out_tok=torch.empty_like(st.ctx.tok))
@@ -134,31 +130,6 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
     torch.cuda.empty_cache()
     return dict(ms=ms, tok_s=batch / ms * 1e3, bytes=step_bytes, ctx_mean=ctx_mean, launches=launches_per_step,
                 clocks=cs.summary())
-
-
-def start_in_pieces(torch, backend, runner, prompts, params, piece=8):
-    """Same as GpuBackend.start but the prompts are prefilled ``piece`` sequences at a time."""
-    slots = []
-    for p in prompts:
-        slots.append(runner.begin())
-        runner.cache.reserve(slots[-1], len(p) + params.max_new_tokens)
-    backend.seqs = [dict(slot=s, token=0, pos=len(p), temperature=0.0, seed=0, prompt_len=len(p))
-                    for s, p in zip(slots, prompts)]
-    backend.max_len = max(len(p) for p in prompts) + params.max_new_tokens
-    backend.state = backend._state(len(prompts), backend.max_len)
-    backend.state.fill(backend.seqs)
-    st = backend.state
-    with torch.inference_mode():
-        for i in range(0, len(prompts), piece):
-            part = list(range(i, min(i + piece, len(prompts))))
-            ctx = runner.context([(slots[j], prompts[j], [len(prompts[j]) - 1]) for j in part])
-            logits = runner.model.forward(ctx, runner.cache)
-            for j in part:
-                runner.cache.commit(slots[j], len(prompts[j]))
-            st.sampler(logits, st.temps[i:i + len(part)], st.seeds[i:i + len(part)], ctx.row_pos, ctx.want_rows,
-                       st.ctx.tok[i:i + len(part)], False)
-    backend.live = list(range(len(prompts)))
-    return st.read(len(prompts))
 
 
 def time_prefill(torch, dk, model, tokens, iters=3):

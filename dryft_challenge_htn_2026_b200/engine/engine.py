@@ -38,11 +38,15 @@ def random_model(config, seed=0, dtype=torch.bfloat16, device="cuda"):
 
 
 class Engine:
-    def __init__(self, model_path=None, dtype=torch.bfloat16, model=None, max_tokens=None, use_graph=True):
+    def __init__(self, model_path=None, dtype=torch.bfloat16, model=None, max_tokens=None, use_graph=True,
+                 max_prefill_tokens=32768):
         """``model_path``: folder with config.json and safetensors (or pass a built ``model``).
-        ``max_tokens``: cache size in tokens; by default the cache is sized by each call."""
+        ``max_tokens``: cache size in tokens; by default the cache is sized by each call.
+        ``max_prefill_tokens``: most prompt tokens one step runs; a batch of prompts beyond it is
+        prefilled in several steps (whole sequences, a longer one in chunks), with equal results."""
         self.model = model if model is not None else load_model(model_path, dtype)
         self.use_graph = use_graph
+        self.max_prefill_tokens = max_prefill_tokens
         self.runner = None
         self.backend = None
         self._fixed_tokens = max_tokens
@@ -53,7 +57,7 @@ class Engine:
         self.backend = self.runner = None   # drop the old cache before the new one is allocated
         torch.cuda.empty_cache()
         self.runner = Runner(self.model, tokens, slots)
-        self.backend = GpuBackend(self.runner, self.use_graph)
+        self.backend = GpuBackend(self.runner, self.use_graph, self.max_prefill_tokens)
 
     def _ensure(self, prompts, max_new_tokens):
         need = sum((len(p) + max_new_tokens + PAGE - 1) // PAGE * PAGE for p in prompts)

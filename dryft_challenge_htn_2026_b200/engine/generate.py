@@ -207,8 +207,9 @@ class GpuBackend:
     """``run_batch``'s backend on the real model. One instance serves many batches one after
     another; decode states (and their graphs) are kept per (rows, table width)."""
 
-    def __init__(self, runner, use_graph=True):
+    def __init__(self, runner, use_graph=True, max_prefill_tokens=32768):
         self.runner, self.use_graph = runner, use_graph
+        self.max_prefill_tokens = max_prefill_tokens   # most prompt tokens one step runs (bounds the activations)
         self.states = {}
         self.prepared = 0
         self.seqs = None
@@ -224,6 +225,27 @@ class GpuBackend:
         if st is None:
             st = self.states[(rows, width)] = DecodeState(self.runner, rows, width)
         return st
+
+    def _prefill_plan(self, lengths):
+        """Steps of the prefill: each a list of (sequence, first token, end token). Whole sequences
+        are taken in order while they fit ``max_prefill_tokens``; a longer one is cut into chunks."""
+        limit = max(1, self.max_prefill_tokens)
+        steps, cur, used = [], [], 0
+        for i, n in enumerate(lengths):
+            if n > limit:
+                if cur:
+                    steps.append(cur)
+                    cur, used = [], 0
+                steps += [[(i, p0, min(n, p0 + limit))] for p0 in range(0, n, limit)]
+                continue
+            if used + n > limit:
+                steps.append(cur)
+                cur, used = [], 0
+            cur.append((i, 0, n))
+            used += n
+        if cur:
+            steps.append(cur)
+        return steps
 
     @torch.inference_mode()
     def start(self, prompts, params, seeds):
@@ -241,18 +263,22 @@ class GpuBackend:
         self.seqs = [dict(slot=s, token=0, pos=len(p), temperature=params.temperature, seed=sd, prompt_len=len(p))
                      for s, p, sd in zip(slots, prompts, seeds)]
         self.max_len = max(len(p) for p in prompts) + params.max_new_tokens
-        self.state = self._state(len(prompts), self.max_len)
-        ctx = r.context([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-        logits = r.model.forward(ctx, r.cache)
-        for s, p in zip(slots, prompts):
-            r.cache.commit(s, len(p))
-        api.gemm_tc_check()
-        st = self.state
+        st = self.state = self._state(len(prompts), self.max_len)
         st.fill(self.seqs)
-        n = len(prompts)
-        st.sampler(logits, st.temps[:n], st.seeds[:n], ctx.row_pos, ctx.want_rows, st.ctx.tok[:n], False)
-        self.live = list(range(n))
-        return st.read(n)
+        for step in self._prefill_plan([len(p) for p in prompts]):
+            # logits only where a prompt ends; the first token of those sequences is sampled at once
+            ended = [i for i, _, p1 in step if p1 == len(prompts[i])]
+            ctx = r.context([(slots[i], prompts[i][p0:p1], [p1 - p0 - 1] if p1 == len(prompts[i]) else [])
+                             for i, p0, p1 in step])
+            logits = r.model.forward(ctx, r.cache)
+            for i, p0, p1 in step:
+                r.cache.commit(slots[i], p1 - p0)
+            if ended:
+                lo, hi = ended[0], ended[-1] + 1          # sequences are taken in order: a contiguous range
+                st.sampler(logits, st.temps[lo:hi], st.seeds[lo:hi], ctx.row_pos, ctx.want_rows, st.ctx.tok[lo:hi], False)
+        api.gemm_tc_check()
+        self.live = list(range(len(prompts)))
+        return st.read(len(prompts))
 
     @torch.inference_mode()
     def decode(self):

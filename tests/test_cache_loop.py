@@ -233,3 +233,21 @@ def test_request_seeds_are_distinct_and_fit_two_words():
     assert ((lo & 0xFFFFFFFF) | ((hi & 0xFFFFFFFF) << 32)) == request_seed(5, 3)
     with pytest.raises(ValueError):
         SamplingParams(4, temperature=-1.0)
+
+
+def test_prefill_plan_groups_whole_sequences_and_chunks_long_ones():
+    from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
+    plan = GpuBackend(None, max_prefill_tokens=100)._prefill_plan
+    assert plan([10, 20, 30]) == [[(0, 0, 10), (1, 0, 20), (2, 0, 30)]]
+    assert plan([60, 50, 40, 100]) == [[(0, 0, 60)], [(1, 0, 50), (2, 0, 40)], [(3, 0, 100)]]
+    assert plan([30, 250, 5]) == [[(0, 0, 30)], [(1, 0, 100)], [(1, 100, 200)], [(1, 200, 250)], [(2, 0, 5)]]
+    for lens in ([1], [100, 100], [101, 99, 1, 300], [7] * 40):
+        steps = plan(lens)
+        covered = {}
+        for step in steps:
+            assert sum(p1 - p0 for _, p0, p1 in step) <= 100
+            assert [i for i, _, _ in step] == sorted(i for i, _, _ in step)
+            for i, p0, p1 in step:
+                assert p0 == covered.get(i, 0) and p1 > p0       # every sequence front to back without gaps
+                covered[i] = p1
+        assert [covered[i] for i in range(len(lens))] == lens

@@ -150,3 +150,15 @@ def test_products_that_add_into_the_residual_and_apply_the_deferred_norm(tmp_pat
     scale = max(1.0, float(plain.forward(cfg, t, prompts[1]).abs().max()))
     for i, p in enumerate(prompts):
         assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale
+
+
+def test_prefill_in_several_steps_gives_the_same_tokens(tmp_path):
+    """Prompts that do not fit one prefill step (here: a limit of 50 tokens) are prefilled in groups of
+    whole sequences and a long one in chunks; in float32 that changes no token."""
+    folder = make_folder(tmp_path, "C", seed=13)
+    prompts = [random_tokens(TINY["C"]["vocab_size"], L, 60 + i) for i, L in enumerate([20, 25, 130, 7, 49, 51])]
+    whole = list(dk.Engine(folder, dtype=torch.float32).generate(prompts, 10, temperature=0.8, seed=4))
+    pieces = list(dk.Engine(folder, dtype=torch.float32, max_prefill_tokens=50).generate(prompts, 10, temperature=0.8, seed=4))
+    assert pieces == whole
+    bf = list(dk.Engine(folder, dtype=torch.bfloat16, max_prefill_tokens=50).generate(prompts, 10))
+    assert len(bf) == 10 and all(len(s) == len(prompts) for s in bf)
