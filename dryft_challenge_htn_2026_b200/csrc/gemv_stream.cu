@@ -10,8 +10,11 @@
 // rows into its own two-deep ring in shared memory with cp.async (one instruction per row: the 32
 // lanes fetch 512 contiguous bytes of that row, and the next stages continue the same rows) and
 // multiplies from shared memory on the tensor cores (ldmatrix + mma.sync, float32 accumulation).
-// At the end of a tile the four warps add their sums through shared memory. There is no waiting
-// on flags: the only waits are cp.async.wait_group and block barriers.
+// At the end of a tile the four warps leave their sums in shared memory for a fifth warp, which adds
+// them up, applies the epilogue and stores, while the four go on streaming the next tile (two
+// buffers, handed over with named barriers: waiting for the slowest warp at every tile cost 11 to
+// 17 % of the kernel). There is no waiting on flags: the only waits are cp.async.wait_group and
+// block barriers.
 //
 // Programmatic dependent launch: every warp issues the weight copies of its first stages before it
 // waits for the previous kernel (weights never depend on it); x is fetched after the wait.
@@ -115,20 +118,35 @@ struct Fuse {
 // gridDim.x is a multiple of SK: block b has slice b % SK and tiles b / SK, + gridDim.x / SK, ...
 // (Dealing the rows out evenly instead, in tiles of unequal heights, was measured 15 % slower: the
 // bytes a ring slot holds in flight shrink with the tile, and the kernel lives on bytes in flight.)
+__device__ __forceinline__ void bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory"); }
+
+// FUSE 0 and 1 run with a fifth warp for the epilogues; FUSE 2, whose epilogue meets other blocks,
+// keeps the four warps doing it together.
+template <int FUSE> struct Shape {
+    static constexpr bool EPI = FUSE != 2;
+    static constexpr int THREADS = (WARPS + (EPI ? 1 : 0)) * 32;
+    static constexpr int RED_BUFS = EPI ? 2 : 1;
+};
+
 template <int MR, int MODE, int FUSE>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(Shape<FUSE>::THREADS)
 gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* ws, int M, int N, int K, int SK,
                    int tiles, Fuse fu) {
     __shared__ float rstd_s[16];
     __shared__ int last_flag;
+    constexpr bool EPI = Shape<FUSE>::EPI;
+    constexpr int THREADS = Shape<FUSE>::THREADS;
+    constexpr int RED = WARPS * WR * MR;      // floats of one buffer of the warps' sums
     constexpr int OUTS = MODE == 2 ? 8 : 16;  // outputs per tile
     constexpr int NT = MR / 8;                // 8-wide batch tiles
     extern __shared__ __align__(128) uint8_t smem[];
-    float* red = reinterpret_cast<float*>(smem + WARPS * DEPTH * STAGE_BYTES);  // [WARPS][WR][MR]
-    uint8_t* xs = reinterpret_cast<uint8_t*>(red + WARPS * WR * MR);           // [MR][slice] rows of x
+    float* red = reinterpret_cast<float*>(smem + WARPS * DEPTH * STAGE_BYTES);  // [RED_BUFS][WARPS][WR][MR]
+    uint8_t* xs = reinterpret_cast<uint8_t*>(red + Shape<FUSE>::RED_BUFS * RED);  // [MR][slice] rows of x
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t ring = smem_u32(smem + warp * DEPTH * STAGE_BYTES);
+    const bool is_epi = EPI && warp == WARPS; // the epilogue warp: fetches and multiplies nothing
+    const uint32_t ring = smem_u32(smem + (is_epi ? 0 : warp) * DEPTH * STAGE_BYTES);
 
     const int slice = blockIdx.x % SK;
     const int per = slice_len(K, SK);
@@ -156,16 +174,17 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
 
     // prologue: the first DEPTH stages of this warp, before the dependency wait
     int head = warp;                          // next block stage this warp fetches
-    for (int d = 0; d < DEPTH; d++, head += WARPS) {
-        if (head < total) fetch(head, d);
-        cp_async_commit();
-    }
+    if (!is_epi)
+        for (int d = 0; d < DEPTH; d++, head += WARPS) {
+            if (head < total) fetch(head, d);
+            cp_async_commit();
+        }
     // The next product's weights: asked into L2 now, so that HBM keeps streaming through the short
     // kernels that follow and that product starts on warm lines. Pieces are dealt round-robin.
     if (fu.pf_bytes) {
         constexpr size_t PIECE = 16384;
         const size_t n = (fu.pf_bytes + PIECE - 1) / PIECE;
-        for (size_t i = (size_t)tid * gridDim.x + blockIdx.x; i < n; i += (size_t)gridDim.x * WARPS * 32) {
+        for (size_t i = (size_t)tid * gridDim.x + blockIdx.x; i < n; i += (size_t)gridDim.x * THREADS) {
             const size_t off = i * PIECE;
             const unsigned sz = (unsigned)(fu.pf_bytes - off < PIECE ? (fu.pf_bytes - off) & ~(size_t)15 : PIECE);
             if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(fu.pf + off), "r"(sz) : "memory");
@@ -187,7 +206,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         for (int r = 0; r < MR / WARPS; r++) {   // sums of squares: warp w has rows w, w + 4, ...
             const int j = warp + r * WARPS;
             float ss = 0.f;
-            if (j < M)
+            if (j < M && !is_epi)
 #pragma unroll 8
                 for (int i = lane; i < fu.sq_tiles; i += 32) ss += __ldcg(fu.sq_in + i * 16 + j);
             ssr[r] = ss;
@@ -205,14 +224,14 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                 }
             }
         };
-        request(tid);
+        if (!is_epi) request(tid);
 #pragma unroll
         for (int r = 0; r < MR / WARPS; r++) {
             const float ss = warp_sum(ssr[r]);
-            if (lane == 0 && warp + r * WARPS < M) rstd_s[warp + r * WARPS] = rsqrtf(ss / (float)K + fu.eps);
+            if (lane == 0 && !is_epi && warp + r * WARPS < M) rstd_s[warp + r * WARPS] = rsqrtf(ss / (float)K + fu.eps);
         }
         __syncthreads();
-        for (int q0 = tid; q0 < row_quads; q0 += CG * WARPS * 32) {
+        for (int q0 = is_epi ? row_quads : tid; q0 < row_quads; q0 += CG * WARPS * 32) {
 #pragma unroll
             for (int c = 0; c < CG; c++) {
                 const int q = q0 + c * WARPS * 32;
@@ -239,7 +258,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         const int row_chunks = klen / 8;      // 16-byte chunks per row
         const int total = M * row_chunks;
         const int rot = (int)(((long long)blockIdx.x * total) / gridDim.x) & ~31;   // see above: spread the blocks over L2
-        for (int c0 = tid; c0 < total; c0 += WARPS * 32) {
+        for (int c0 = tid; c0 < total; c0 += THREADS) {
             const int c = c0 + rot < total ? c0 + rot : c0 + rot - total;
             const int m = c / row_chunks, j = c % row_chunks;
             cp_async16(smem_u32(xs + m * x_stride + j * 16), x + (size_t)m * K + k_begin + j * 8, true);
@@ -258,6 +277,38 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
     const uint32_t a_off = (uint32_t)(((lane & 7) + 8 * ((lane >> 3) & 1)) * ROW_STRIDE + 16 * (lane >> 4));
     const uint32_t b_base = smem_u32(xs) + (uint32_t)(((lane & 7) + (NT == 2 ? 8 * (lane >> 4) : 0)) * x_stride +
                                                       16 * ((lane >> 3) & 1));
+
+    // The epilogue of one tile from the warps' sums in ``sums``: outputs o = first, first + step, ...
+    auto finish_tile = [&](const float* sums, int tile, int first, int step) {
+        for (int o = first; o < OUTS * MR; o += step) {
+            const int i = o % OUTS, j = o / OUTS;
+            const int n = tile * OUTS + i;
+            if (n < N && j < M) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) v += sums[w * (WR * MR) + i * MR + j];
+                if (MODE == 2) {
+                    float up = 0.f;
+#pragma unroll
+                    for (int w = 0; w < WARPS; w++) up += sums[w * (WR * MR) + (8 + i) * MR + j];
+                    v = v / (1.f + expf(-v)) * up;
+                }
+                if (SK > 1) ws[((size_t)slice * M + j) * N + n] = v;
+                else if (MODE == 1) reinterpret_cast<float*>(out)[(size_t)j * N + n] = v;
+                else reinterpret_cast<bf16*>(out)[(size_t)j * N + n] = __float2bfloat16_rn(v);
+            }
+        }
+    };
+    constexpr int FULL = 1, EMPTY = 3;        // named barriers FULL + buffer, EMPTY + buffer (0 is __syncthreads)
+    if (is_epi) {
+        for (int ti = 0; ti < my_tiles; ti++) {
+            const int buf = ti & 1;
+            bar_sync(FULL + buf, THREADS);    // the four warps have left their sums of tile ti
+            finish_tile(red + buf * RED, tile0 + ti * tile_step, lane, 32);
+            if (ti + 2 < my_tiles) bar_arrive(EMPTY + buf, THREADS);   // the buffer may be written again
+        }
+        return;
+    }
 
     int tail = warp, slot = 0;                // next block stage this warp multiplies, and its ring slot
     for (int ti = 0; ti < my_tiles; ti++) {
@@ -291,8 +342,9 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
             cp_async_wait<DEPTH - 1>();       // this warp's next stage has landed
             __syncwarp();
         }
-        // the four warps hold sums over different k: add them up through shared memory
-        float* mine = red + warp * (WR * MR);
+        // the four warps hold sums over different k: they go to shared memory to be added up
+        float* mine = red + (EPI ? (ti & 1) * RED : 0) + warp * (WR * MR);
+        if (EPI && ti >= 2) bar_sync(EMPTY + (ti & 1), THREADS);   // the epilogue warp is done with tile ti - 2
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
             mine[g * MR + nt * 8 + 2 * t] = acc[0][nt][0] + acc[1][nt][0];
@@ -301,6 +353,11 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
             mine[(g + 8) * MR + nt * 8 + 2 * t + 1] = acc[0][nt][3] + acc[1][nt][3];
 #pragma unroll
             for (int c = 0; c < 4; c++) acc[0][nt][c] = acc[1][nt][c] = 0.f;
+        }
+        if (EPI) {                            // hand the sums to the epilogue warp and go on with the next tile
+            __threadfence_block();
+            bar_arrive(FULL + (ti & 1), THREADS);
+            continue;
         }
         __syncthreads();
         if (FUSE == 2) {
@@ -350,24 +407,8 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                     if (i == 0 && j < M) fu.sq_out[(size_t)tile * 16 + j] = sq;
                 }
             }
-        } else
-        for (int o = tid; o < OUTS * MR; o += WARPS * 32) {
-            const int i = o % OUTS, j = o / OUTS;
-            const int n = tile * OUTS + i;
-            if (n < N && j < M) {
-                float v = 0.f;
-#pragma unroll
-                for (int w = 0; w < WARPS; w++) v += red[w * (WR * MR) + i * MR + j];
-                if (MODE == 2) {
-                    float up = 0.f;
-#pragma unroll
-                    for (int w = 0; w < WARPS; w++) up += red[w * (WR * MR) + (8 + i) * MR + j];
-                    v = v / (1.f + expf(-v)) * up;
-                }
-                if (SK > 1) ws[((size_t)slice * M + j) * N + n] = v;
-                else if (MODE == 1) reinterpret_cast<float*>(out)[(size_t)j * N + n] = v;
-                else reinterpret_cast<bf16*>(out)[(size_t)j * N + n] = __float2bfloat16_rn(v);
-            }
+        } else {
+            finish_tile(red, tile, tid, WARPS * 32);
         }
         __syncthreads();
     }
@@ -378,7 +419,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
 template <int MR, int MODE, int FUSE>
 int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int K, int SK, int blocks, const Fuse& fu,
            cudaStream_t st) {
-    const size_t smem = (size_t)WARPS * DEPTH * STAGE_BYTES + (size_t)WARPS * WR * MR * sizeof(float) +
+    const size_t smem = (size_t)WARPS * DEPTH * STAGE_BYTES + (size_t)Shape<FUSE>::RED_BUFS * WARPS * WR * MR * sizeof(float) +
                         (size_t)MR * (slice_len(K, SK) * 2 + 16);
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
@@ -390,7 +431,7 @@ int launch(const bf16* x, const bf16* W, void* out, float* ws, int M, int N, int
     const int tiles = MODE == 2 ? (N + 7) / 8 : (N + 15) / 16;
     blocks = blocks / SK * SK;
     if (blocks > tiles * SK) blocks = tiles * SK;
-    return dk_launch(gemv_stream_kernel<MR, MODE, FUSE>, dim3(blocks), dim3(WARPS * 32), smem, st, x, W, out, ws, M, N, K,
+    return dk_launch(gemv_stream_kernel<MR, MODE, FUSE>, dim3(blocks), dim3(Shape<FUSE>::THREADS), smem, st, x, W, out, ws, M, N, K,
                      SK, tiles, fu);
 }
 
