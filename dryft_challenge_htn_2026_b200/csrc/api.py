@@ -224,38 +224,31 @@ def decode_splits(n_seq, n_kv_heads, group, max_splits=16, resident_blocks=2 * 1
 
 
 def attention_decode_ws(n_seq, n_heads, head_dim, nsplit, device):
-    """Scratch for attention_decode_bf16: float32 partial outputs and (max, sum) pairs."""
-    if nsplit == 1:
-        return None, None
-    return (torch.empty(n_seq * n_heads * nsplit * head_dim, dtype=torch.float32, device=device),
-            torch.empty(n_seq * n_heads * nsplit * 2, dtype=torch.float32, device=device))
+    """Scratch for attention_decode_bf16: float32 partial outputs and (max, sum) pairs, one per warp
+    of every block: 4 * nsplit a head."""
+    parts = 4 * nsplit
+    return (torch.empty(n_seq * n_heads * parts * head_dim, dtype=torch.float32, device=device),
+            torch.empty(n_seq * n_heads * parts * 2, dtype=torch.float32, device=device))
 
 
 def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads, n_kv_heads, head_dim, window, scale,
-                          nsplit, ws_acc=None, ws_ml=None, merge_in_kernel=False):
-    """One query token per sequence over its cached keys [.., row_pos] (tensor cores, keys split
-    over ``nsplit`` blocks and merged by a second kernel, or with ``merge_in_kernel`` by the last
-    block of each head group in the same launch: 1.5 to 5 us slower on B200, the tickets cost more
-    than the dependent launch)."""
+                          nsplit, ws_acc, ws_ml):
+    """One query token per sequence over its cached keys [.., row_pos] (tensor cores). The keys are
+    split over ``nsplit`` blocks of four warps; every warp leaves a partial result and a second
+    kernel merges the 4 * nsplit of a head."""
     _need(q, "q", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
+    _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
     n_seq = q.shape[0]
-    if not 1 <= nsplit <= 32:
-        raise KernelError(f"attention_decode_bf16: {nsplit} splits, the merge takes 1 to 32")
-    if nsplit > 1:
-        _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
-        if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * nsplit * head_dim \
-                or ws_ml.numel() < n_seq * n_heads * nsplit * 2:
-            raise KernelError("attention_decode_bf16: scratch too small for this batch and split count")
+    if not 1 <= nsplit <= 16:
+        raise KernelError(f"attention_decode_bf16: {nsplit} splits, the merge takes 1 to 16")
+    if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * 4 * nsplit * head_dim \
+            or ws_ml.numel() < n_seq * n_heads * 4 * nsplit * 2:
+        raise KernelError("attention_decode_bf16: scratch too small for this batch and split count")
     lib = _attn_lib(head_dim)
-    counters = None
-    if 1 < nsplit <= 32 and merge_in_kernel:
-        group = n_heads // max(1, n_kv_heads)
-        counters = tile_counters(q.device, n_seq * n_kv_heads * ((group + 15) // 16))
     _check(lib, lib.dk_attn_decode_bf16(_p(q), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store), _p(row_pos),
                                         _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
-                                        int(window or 0), c_float(scale), nsplit, _p(counters), _stream()),
-           "attention_decode_bf16", 2 if nsplit > 1 and counters is None else 1)
+                                        int(window or 0), c_float(scale), nsplit, _stream()), "attention_decode_bf16", 2)
 
 
 # ---------------------------------------------------------------------------------------- products

@@ -6,8 +6,8 @@
 //    and one query head (4 warps x 16 rows) and walks the key pages up to its diagonal.
 //  * decode: one query token per sequence; a block owns the (up to 16) query heads that share a
 //    kv head and one split of the keys; its 4 warps take 16 keys each of every 64-key page, each
-//    through a cp.async ring of its own (2 or 3 chunks deep), and are merged through shared memory;
-//    splits are merged by the combine kernel.
+//    through a cp.async ring of its own (2 or 3 chunks deep), and each leaves a partial result of
+//    its own; the combine kernel merges the 4 x splits partial results of a head.
 // Prefill stages key/value pages ([64, HD] per kv head, contiguous) with cp.async, two stages deep. P is rounded to bfloat16 before P.V; row sums use the unrounded values.
 // Reference formulas: engine/fused.py:301-343 (prefill), :478-565 (split decode + combine).
 #include "common.cuh"
@@ -237,11 +237,9 @@ attn_prefill_kernel(const bf16* q, bf16* out, const bf16* k_store, const bf16* v
 // ws_acc [(b*nh + head)*nsplit + split][HD] and ws_ml [...][2] = (max in log2 domain, row sum).
 template <int D>
 __global__ void __launch_bounds__(128)
-attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
-                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
-                   int* counters) {
+attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_store, const bf16* v_store,
+                   const int* row_pos, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2) {
     extern __shared__ __align__(16) bf16 smem[];
-    __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
     const int split = blockIdx.x, nsplit = gridDim.x;
@@ -315,135 +313,63 @@ attn_decode_kernel(const bf16* q, bf16* out, float* ws_acc, float* ws_ml, const 
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
         l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     }
-    // merge the four warps (each saw different keys) through shared memory
-    float* sm_m = reinterpret_cast<float*>(smem);  // [4][16]
-    float* sm_l = sm_m + 64;                       // [4][16]
-    float* sm_a = sm_l + 64;                       // [4][16][HD]
-    __syncthreads();
-    if (t == 0) {
-        sm_m[warp * 16 + g] = m[0];
-        sm_m[warp * 16 + g + 8] = m[1];
-        sm_l[warp * 16 + g] = l[0];
-        sm_l[warp * 16 + g + 8] = l[1];
-    }
+    // Every warp saw different keys and stores its own partial result: part 4 * split + warp of
+    // 4 * nsplit a head. (Adding the four up inside the block first, through shared memory and two
+    // block barriers, cost 3.8 us of the kernel's 18.)
+    const int parts = 4 * nsplit, part = 4 * split + warp;
 #pragma unroll
-    for (int nt = 0; nt < HD / 8; nt++) {
-        float* a0 = sm_a + ((size_t)(warp * 16 + g) * HD) + nt * 8 + 2 * t;
-        float* a1 = sm_a + ((size_t)(warp * 16 + g + 8) * HD) + nt * 8 + 2 * t;
-        a0[0] = acc[nt][0];
-        a0[1] = acc[nt][1];
-        a1[0] = acc[nt][2];
-        a1[1] = acc[nt][3];
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < heads_here * HD; idx += blockDim.x) {
-        const int row = idx / HD, d = idx % HD;
-        float M = -INFINITY;
+    for (int r = 0; r < 2; r++) {
+        const int row = g + 8 * r;
+        if (row < heads_here) {
+            const size_t at = ((size_t)b * nh + head0 + row) * parts + part;
+            float* dst = ws_acc + at * HD + 2 * t;
 #pragma unroll
-        for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + row]);
-        float L = 0.f, A = 0.f;
-        if (M != -INFINITY) {
-#pragma unroll
-            for (int w = 0; w < 4; w++) {
-                const float f = exp2f(sm_m[w * 16 + row] - M);
-                L += sm_l[w * 16 + row] * f;
-                A += sm_a[(size_t)(w * 16 + row) * HD + d] * f;
-            }
-        }
-        const size_t head = (size_t)b * nh + head0 + row;
-        if (nsplit == 1) {
-            out[head * HD + d] = __float2bfloat16_rn(L > 0.f ? A / L : 0.f);
-        } else {
-            ws_acc[(head * nsplit + split) * HD + d] = A;
-            if (d == 0) {
-                ws_ml[(head * nsplit + split) * 2] = M;
-                ws_ml[(head * nsplit + split) * 2 + 1] = L;
-            }
-        }
-    }
-    if (nsplit == 1 || counters == nullptr) return;
-    // the block that draws the last ticket of this (sequence, kv head, head tile) merges the splits
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int* c = counters + ((size_t)b * nkv + kvh) * mtiles + mt;
-        const int ticket = atomicAdd(c, 1);
-        is_last = ticket == nsplit - 1;
-        if (is_last) *c = 0;  // everyone has drawn: ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // one warp per head; lane s holds split s's (max, sum) (nsplit <= 32 here), and the loads of
-    // the partial outputs do not depend on one another, so they are all in flight together
-    for (int row = warp; row < heads_here; row += 4) {
-        const size_t head = (size_t)b * nh + head0 + row;
-        const float* ml = ws_ml + head * nsplit * 2;
-        const float* wa = ws_acc + head * nsplit * HD;
-        const float Ms = lane < nsplit ? __ldcg(ml + 2 * lane) : -INFINITY;
-        const float Ls = lane < nsplit ? __ldcg(ml + 2 * lane + 1) : 0.f;
-        float M = Ms;
-#pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
-        const float fs = M == -INFINITY ? 0.f : exp2f(Ms - M);   // this split's weight
-        float L = Ls * fs;
-#pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        for (int base = 0; base < HD; base += 64) {
-            const int d0 = base + lane * 2;
-            const bool ok = d0 < HD;
-            float a0 = 0.f, a1 = 0.f;
-#pragma unroll 8
-            for (int s = 0; s < nsplit; s++) {
-                const float f = __shfl_sync(0xffffffffu, fs, s);
-                const float2 v = ok ? __ldcg(reinterpret_cast<const float2*>(wa + (size_t)s * HD + d0)) : make_float2(0.f, 0.f);
-                a0 += v.x * f;
-                a1 += v.y * f;
-            }
-            if (ok) *reinterpret_cast<uint32_t*>(out + head * HD + d0) = pack_bf16(a0 * inv, a1 * inv);
+            for (int nt = 0; nt < HD / 8; nt++) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(acc[nt][2 * r], acc[nt][2 * r + 1]);
+            if (t == 0) *reinterpret_cast<float2*>(ws_ml + at * 2) = make_float2(m[r], l[r]);
         }
     }
 }
 
-// grid (sequences * nh / 4), 128 threads: a warp merges the splits of one head. Lane s holds split
-// s's (max, sum); the partial outputs of the first 8 splits are requested together with them, so
-// up to 8 splits cost one trip to memory after the wait (nsplit <= 32).
+// grid (sequences * nh / 4), 128 threads: a warp merges the parts of one head (at most 64). Lane s
+// holds the (max, sum) of parts s and s + 32; the partial outputs of the first 16 parts are requested
+// together with them, so up to 16 parts cost one trip to memory after the wait.
 __global__ void __launch_bounds__(128)
-attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int nsplit, int n_heads) {
+attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int parts, int n_heads) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const size_t head = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (head >= (size_t)n_heads) return;
-    const float* ml = ws_ml + head * nsplit * 2;
-    const float* wa = ws_acc + head * nsplit * HD;
-    const float Ms = lane < nsplit ? ml[2 * lane] : -INFINITY;
-    const float Ls = lane < nsplit ? ml[2 * lane + 1] : 0.f;
-    float fs = 0.f, inv = 0.f;
+    const float2* ml = reinterpret_cast<const float2*>(ws_ml) + head * parts;
+    const float* wa = ws_acc + head * parts * HD;
+    const float2 none = make_float2(-INFINITY, 0.f);
+    const float2 p0 = lane < parts ? ml[lane] : none, p1 = lane + 32 < parts ? ml[lane + 32] : none;
+    float f0 = 0.f, f1 = 0.f, inv = 0.f;
     for (int base = 0; base < HD; base += 128) {
         const int d0 = base + lane * 4;
         const bool ok = d0 < HD;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int s0 = 0; s0 < nsplit; s0 += 8) {
-            float4 v[8];
+        for (int s0 = 0; s0 < parts; s0 += 16) {
+            float4 v[16];
 #pragma unroll
-            for (int u = 0; u < 8; u++)
-                v[u] = ok && s0 + u < nsplit ? *reinterpret_cast<const float4*>(wa + (size_t)(s0 + u) * HD + d0)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (base == 0 && s0 == 0) {       // the weights of the splits, once
-                float M = Ms;
+            for (int u = 0; u < 16; u++)
+                v[u] = ok && s0 + u < parts ? *reinterpret_cast<const float4*>(wa + (size_t)(s0 + u) * HD + d0)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (base == 0 && s0 == 0) {       // the weights of the parts, once
+                float M = fmaxf(p0.x, p1.x);
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
-                fs = M == -INFINITY ? 0.f : exp2f(Ms - M);
-                float L = Ls * fs;
+                f0 = M == -INFINITY ? 0.f : exp2f(p0.x - M);
+                f1 = M == -INFINITY ? 0.f : exp2f(p1.x - M);
+                float L = p0.y * f0 + p1.y * f1;
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
                 inv = L > 0.f ? 1.f / L : 0.f;
             }
+            const float fsrc = s0 < 32 ? f0 : f1;   // a run of 16 parts lies in one half
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const float f = __shfl_sync(0xffffffffu, fs, (s0 + u) & 31);
+            for (int u = 0; u < 16; u++) {
+                const float f = __shfl_sync(0xffffffffu, fsrc, (s0 + u) & 31);
                 a.x += v[u].x * f, a.y += v[u].y * f, a.z += v[u].z * f, a.w += v[u].w * f;
             }
         }
@@ -484,14 +410,12 @@ DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store
                      window, scale * 1.4426950408889634f);
 }
 
-// ws_acc: n_seq*nh*nsplit*HD floats, ws_ml: n_seq*nh*nsplit*2 floats (unused when nsplit == 1).
-// counters: null (a second kernel merges the splits) or n_seq * nkv * ceil(G / 16) zeroed ints (the
-// last block of each head group merges them in the same launch and leaves the counters zero).
+// ws_acc: n_seq * nh * 4 * nsplit * HD floats, ws_ml: n_seq * nh * 4 * nsplit * 2 floats: every warp of a
+// block leaves a partial result of its own, the merge kernel adds up the 4 * nsplit of a head (nsplit <= 16).
 DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float* ws_ml, const void* k_store,
                                   const void* v_store, const int* row_pos, const int* page_table, int pt_stride,
-                                  int n_seq, int nh, int nkv, int window, float scale, int nsplit, int* counters,
-                                  cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1 || nsplit > 32) return (int)cudaErrorInvalidValue;
+                                  int n_seq, int nh, int nkv, int window, float scale, int nsplit, cudaStream_t st) {
+    if (nh % nkv != 0 || nsplit < 1 || nsplit > 16 || ws_acc == nullptr || ws_ml == nullptr) return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;
@@ -502,15 +426,15 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
     const long long blocks = (long long)nsplit * nkv * mtiles * n_seq;
     if (blocks <= 2LL * sms && 2 * (decode_smem(3) + 1024) <= 227 * 1024)
         e = dk_launch(attn_decode_kernel<3>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(3), st, (const bf16*)q,
-                      (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
-                      nh, nkv, window, scale * 1.4426950408889634f, counters);
+                      ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
+                      window, scale * 1.4426950408889634f);
     else
         e = dk_launch(attn_decode_kernel<2>, dim3(nsplit, nkv * mtiles, n_seq), dim3(128), decode_smem(2), st, (const bf16*)q,
-                      (bf16*)out, ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride,
-                      nh, nkv, window, scale * 1.4426950408889634f, counters);
-    if (e || nsplit == 1 || counters != nullptr) return e;   // (callers give counters only for nsplit <= 32)
+                      ws_acc, ws_ml, (const bf16*)k_store, (const bf16*)v_store, row_pos, page_table, pt_stride, nh, nkv,
+                      window, scale * 1.4426950408889634f);
+    if (e) return e;
     return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
-                     (const float*)ws_ml, (bf16*)out, nsplit, n_seq * nh);
+                     (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh);
 }
 
 // ------------------------------------------------------------------------------- fused decode
@@ -730,7 +654,7 @@ attn_decode_fused_kernel(const bf16* qkv, const float* parts, int n_parts, size_
 }
 
 // qkv [n_seq, (nh + 2 nkv) * HD] bf16, or parts != null: n_parts float32 partial sums of it
-// (part_stride elements apart). ws_acc / ws_ml as dk_attn_decode_bf16; counters: n_seq * nkv *
+// (part_stride elements apart). ws_acc: n_seq*nh*nsplit*HD floats, ws_ml: n_seq*nh*nsplit*2; counters: n_seq * nkv *
 // ceil(G / 16) ints, zeroed once by the caller (the kernel leaves them zero).
 DK_EXPORT int dk_attn_decode_fused(const void* qkv, const float* parts, int n_parts, long long part_stride, const float* qn,
                                    const float* kn, const float* cos_t, const float* sin_t, float eps, void* out,
