@@ -34,22 +34,46 @@ __global__ void sample_partial_kernel(const float* logits, int V, const float* t
                                       float* ws_val, int* ws_idx) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    pdl_wait();
-    pdl_launch_dependents();
+    // positions, temperatures and seeds are not written by the kernel before this one (the head):
+    // they are fetched before the wait for it
     const int b = blockIdx.y, chunk = blockIdx.x;
     const int p = pos[rows ? rows[b] : b];
     const float temp = temperature[b];
     const uint32_t s_lo = seeds[2 * b], s_hi = seeds[2 * b + 1];
+    pdl_wait();
+    pdl_launch_dependents();
     const float* row = logits + (size_t)b * V;
     const int begin = chunk * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
     float bv = -INFINITY;
     int bi = begin;
     if (p >= 0) {
         const float inv_t = temp > 0.f ? 1.f / temp : 1.f;
-        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-            float z = row[i];
-            if (temp > 0.f) z = z * inv_t + gumbel(s_lo, s_hi, (uint32_t)(p + 1), (uint32_t)i);
-            better(bv, bi, z, i);
+        if (V % 4 == 0 && blockDim.x * 16 == SAMPLE_CHUNK) {
+            // 16 logits a thread, requested together as four 16-byte loads before any is looked at
+            float4 z4[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = begin + (k * (int)blockDim.x + (int)threadIdx.x) * 4;
+                z4[k] = i < end ? *reinterpret_cast<const float4*>(row + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int i = begin + (k * (int)blockDim.x + (int)threadIdx.x) * 4;
+                const float z[4] = {z4[k].x, z4[k].y, z4[k].z, z4[k].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (i + e < end) {
+                        float v = z[e];
+                        if (temp > 0.f) v = v * inv_t + gumbel(s_lo, s_hi, (uint32_t)(p + 1), (uint32_t)(i + e));
+                        better(bv, bi, v, i + e);
+                    }
+            }
+        } else {
+            for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+                float z = row[i];
+                if (temp > 0.f) z = z * inv_t + gumbel(s_lo, s_hi, (uint32_t)(p + 1), (uint32_t)i);
+                better(bv, bi, z, i);
+            }
         }
     }
 #pragma unroll
