@@ -211,7 +211,7 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=16, resident_blocks=2 * 148):
+def decode_splits(n_seq, n_kv_heads, group, max_splits=8, resident_blocks=2 * 148):
     """Number of key splits for decode attention, fixed for a batch size (it must not depend on
     sequence lengths, which change under a captured graph). While all blocks fit the GPU at once
     (two per SM with the three-deep rings): as many splits as keep it so. Beyond that: enough for
