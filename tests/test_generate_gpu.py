@@ -162,3 +162,17 @@ def test_prefill_in_several_steps_gives_the_same_tokens(tmp_path):
     assert pieces == whole
     bf = list(dk.Engine(folder, dtype=torch.bfloat16, max_prefill_tokens=50).generate(prompts, 10))
     assert len(bf) == 10 and all(len(s) == len(prompts) for s in bf)
+
+
+def test_twenty_sequences_decode_on_the_tensor_core_product(tmp_path):
+    """A batch beyond 8 rows takes the tcgen05 decode product (32-row decode state here, 12 of the
+    rows padding after some sequences stop): tokens stay within rounding of the plain implementation."""
+    folder = make_folder(tmp_path, "D", seed=14)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY["D"]["vocab_size"], 3 + (7 * i) % 60, 80 + i) for i in range(20)]
+    eng = dk.Engine(folder, dtype=torch.bfloat16)
+    steps = list(eng.generate(prompts, 12))
+    assert len(steps) == 12 and all(len(s) == 20 for s in steps)
+    scale = max(1.0, float(plain.forward(cfg, t, prompts[5]).abs().max()))
+    for i in (0, 5, 11, 19):
+        assert teacher_forced_gap(cfg, t, prompts[i], [s[i] for s in steps]) <= 0.12 * scale
