@@ -135,6 +135,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
                    int tiles, Fuse fu) {
     __shared__ float rstd_s[16];
     __shared__ int last_flag;
+    __shared__ __align__(8) uint64_t x_bar;   // counts the bytes of x's rows as they land
     constexpr bool EPI = Shape<FUSE>::EPI;
     constexpr int THREADS = Shape<FUSE>::THREADS;
     constexpr int RED = WARPS * WR * MR;      // floats of one buffer of the warps' sums
@@ -189,6 +190,14 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
             const unsigned sz = (unsigned)(fu.pf_bytes - off < PIECE ? (fu.pf_bytes - off) & ~(size_t)15 : PIECE);
             if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(fu.pf + off), "r"(sz) : "memory");
         }
+    }
+    if (FUSE != 1) {
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&x_bar)));
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncthreads();
     }
     GS_NOTE(0);
     pdl_wait();
@@ -255,17 +264,26 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         cp_async_wait<0>();                   // the first weight stages, fetched before the wait
         __syncthreads();
     } else {
-        const int row_chunks = klen / 8;      // 16-byte chunks per row
-        const int total = M * row_chunks;
-        const int rot = (int)(((long long)blockIdx.x * total) / gridDim.x) & ~31;   // see above: spread the blocks over L2
-        for (int c0 = tid; c0 < total; c0 += THREADS) {
-            const int c = c0 + rot < total ? c0 + rot : c0 + rot - total;
-            const int m = c / row_chunks, j = c % row_chunks;
-            cp_async16(smem_u32(xs + m * x_stride + j * 16), x + (size_t)m * K + k_begin + j * 8, true);
+        // One bulk copy a row (the TMA engine, which the weight copies of the rings do not queue in
+        // front of), counted by an mbarrier that every thread waits on.
+        if (tid == 0) {
+            const uint32_t bytes = (uint32_t)klen * 2;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&x_bar)), "r"(bytes * M) : "memory");
+            for (int m = 0; m < M; m++)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                                 smem_u32(xs + m * x_stride)),
+                             "l"(x + (size_t)m * K + k_begin), "r"(bytes), "r"(smem_u32(&x_bar))
+                             : "memory");
         }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
+        cp_async_wait<0>();                   // this thread's weight stages, fetched before the wait
+        const long long t0 = clock64();
+        for (;;) {                            // bounded: a copy of valid rows cannot fail, but nothing here may hang
+            uint32_t ok;
+            asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0; selp.u32 %0, 1, 0, p; }"
+                         : "=r"(ok) : "r"(smem_u32(&x_bar)) : "memory");
+            if (ok || clock64() - t0 > 2000000000LL) break;
+        }
+        __syncwarp();
     }
 
     GS_NOTE(2);
