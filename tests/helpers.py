@@ -27,6 +27,10 @@ TINY = {
     "D": dict(vocab_size=320, hidden_size=128, intermediate_size=192, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=100000.0, tie_word_embeddings=False,
               max_position_embeddings=512),
+    # head size 128 with a window on the upper layers: the tcgen05 attention's window path inside a model
+    "E": dict(vocab_size=264, hidden_size=96, intermediate_size=160, num_hidden_layers=3, num_attention_heads=3,
+              num_key_value_heads=1, head_dim=128, rms_norm_eps=2e-6, rope_theta=20000.0, tie_word_embeddings=True,
+              max_position_embeddings=1024, use_sliding_window=True, sliding_window=150, max_window_layers=1),
 }
 
 
