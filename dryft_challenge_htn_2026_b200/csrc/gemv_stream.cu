@@ -2,7 +2,7 @@
 // out[M,N] = x[M,K] . W[N,K]^T, the same contract and epilogues as gemv_bf16 in gemm.cu
 // (0 store bf16, 1 store float32, 2 W = [gate; up]: store silu(gate)*up; split-K partial sums).
 //
-// Persistent blocks of four warps, two per SM. K is cut into SK slices; block b works on slice
+// Persistent blocks of four streaming warps and an epilogue warp, two per SM. K is cut into SK slices; block b works on slice
 // b % SK only, so its piece of x (at most 16 rows x 2560 elements) is copied into shared memory
 // once and every weight byte that follows is the only traffic. The block walks tiles of 16 weight
 // rows; a tile's slice is cut into stages of 256 elements of K, and stage number i of the block
@@ -17,10 +17,12 @@
 // block barriers.
 //
 // Programmatic dependent launch: every warp issues the weight copies of its first stages before it
-// waits for the previous kernel (weights never depend on it); x is fetched after the wait.
+// waits for the previous kernel (weights never depend on it); x is fetched after the wait, one bulk
+// copy a row by the TMA engine counted on an mbarrier (as 16-byte cp.async pieces, which queue behind
+// the weight copies in the same load path, the rows of x cost 0.5 to 1.7 us of a product).
 //
-// (Measured on the way here: bulk copies of the TMA engine at 512 bytes a request were bound by
-// the engine's request rate; register streaming in the mma fragment layout, which touches 128
+// (Measured on the way here: for the weights, bulk copies of the TMA engine at 512 bytes a request
+// were bound by the engine's request rate; register streaming in the mma fragment layout, which touches 128
 // bytes of 16 rows at a time, stayed near 4.9 TB/s; re-fetching x with every stage cost half as
 // much SM ingress again as the weights.)
 //
