@@ -249,7 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // step made this epilogue 10 us longer
                     if (row < M) {
 #pragma unroll
-                        for (int i = 0; i < 32; i++) f[i] = f[i] / (1.f + __expf(-f[i])) * __uint_as_float(u[i]);
+                        for (int i = 0; i < 32; i++) f[i] = __fdividef(f[i], 1.f + __expf(-f[i])) * __uint_as_float(u[i]);   // 2 ulp: far below the bf16 rounding that follows
                     }
                 }
                 if (row < M && ws != nullptr) {   // float32 partial sums of this slice
