@@ -132,6 +132,43 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
                 clocks=cs.summary())
 
 
+def timeline(torch, dk, api, model, batch):
+    """One decode step inside the captured graph: for every kernel the time from the end of its
+    wait for its predecessor to the end of the next kernel's wait (so overlap is counted once)."""
+    import collections
+
+    import numpy as np
+    from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
+    from dryft_challenge_htn_2026_b200.sampling import SamplingParams
+
+    lens = ragged_lengths(batch, 0)
+    runner = dk.Runner(model, sum((n + 64 + 63) // 64 * 64 for n in lens), max_slots=batch)
+    backend = GpuBackend(runner, use_graph=True)
+    rs = np.random.RandomState(1)
+    backend.start([rs.randint(0, model.spec.vocab_size, n).tolist() for n in lens], SamplingParams(48), [0] * batch).wait()
+    st = backend.state
+    st.capture()
+    for _ in range(32):
+        st.run()
+    torch.cuda.synchronize()
+    api.kernel_trace()
+    st.run()
+    st.run()
+    torch.cuda.synchronize()
+    ev = api.kernel_trace()
+    ev = ev[len(ev) // 2:] + [ev[-1]]                       # the second of the two steps
+    rows = collections.OrderedDict()
+    for a, b in zip(ev[:-1], ev[1:]):
+        rows.setdefault((a[1], int(a[2]), int(a[3])), []).append((b[0] - a[0]) / 1e3)
+    layers = len(model.spec.layers)
+    print(f"decode step at batch {batch}, {layers} layers: {(ev[-1][0] - ev[0][0]) / 1e3:.1f} us, {len(ev) - 1} launches")
+    for (src, grid, block), v in rows.items():
+        print(f"  {src:22s} {grid:6d} x {block:4d}  launches {len(v):4d}  mean {sum(v) / len(v):7.2f} us  total {sum(v):8.1f} us")
+    print("  first layer in order: " + "  ".join(f"{a[1].split('.')[0]}:{(b[0] - a[0]) / 1e3:.1f}" for a, b in list(zip(ev[:-1], ev[1:]))[:10]))
+    backend.finish()
+    return 0
+
+
 def time_prefill(torch, dk, model, tokens, iters=3):
     import numpy as np
     runner = dk.Runner(model, tokens + 64, max_slots=2)
@@ -193,6 +230,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print where one decode step's time goes inside the graph (kernels built with start notes) and exit")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -204,6 +243,8 @@ def main():
         print(f"bench.py: this library runs one model on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(3, args.warmup)
+    if args.timeline:
+        os.environ["DRYFT_KERNEL_TRACE"] = "1"     # read when the package's kernels are built and loaded
 
     import torch
 
@@ -219,6 +260,8 @@ def main():
     model = dk.random_model(cfg, seed=0, dtype=torch.bfloat16)
     pk = peaks()
 
+    if args.timeline:
+        return timeline(torch, dk, api, model, args.batch)
     if args.prefill_only:
         ms, flops = time_prefill(torch, dk, model, PROMPT)
         print(json.dumps({"prefill": {"value": round(PROMPT / ms * 1e3, 1), "tokens": PROMPT, "ms": round(ms, 3),
