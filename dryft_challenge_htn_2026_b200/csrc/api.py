@@ -472,32 +472,31 @@ def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None, prefe
 
 # ------------------------------------------------------------------------------ fused decode mixer
 def attention_decode_fused(qkv, out, q_norm_w, k_norm_w, cos, sin, eps, k_store, v_store, row_pos, page_table, n_heads,
-                           n_kv_heads, head_dim, window, scale, nsplit, ws_acc, ws_ml, counters, write_kv=True):
-    """One launch for a decode step's attention: per-head norm and rotation of the new token's q
-    and k from the projection row (``qkv``: bf16 tensor or ``Partial``), the cache write, attention
-    over the cache in ``nsplit`` splits and their merge. ``counters``: int32 zeros, one per
-    (sequence, kv head, 16-head tile); left zero. Scratch as for ``attention_decode_bf16``."""
+                           n_kv_heads, head_dim, window, scale, nsplit, ws_acc, ws_ml, write_kv=True):
+    """A decode step's attention from the projection row (``qkv``: bf16 tensor or ``Partial``): the
+    attention kernel itself applies the per-head norm and the rotation to the new token's q and k
+    and writes the new key and value to the cache (unless ``write_kv`` is false), so the separate
+    kernel for that is not launched. Splits, scratch and merge as for ``attention_decode_bf16``."""
     n_seq, width = qkv.shape[0], qkv.shape[1]
     qkv, parts, n_parts, stride = _parts(qkv)
     _need(qkv, "qkv", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
     _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
     _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
-    _need(counters, "counters", torch.int32, 1)
+    _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
     if width != (n_heads + 2 * n_kv_heads) * head_dim:
         raise KernelError(f"qkv width {width} != (nh + 2 nkv) * hd")
-    tiles = (n_heads // n_kv_heads + 15) // 16
-    if counters.numel() < n_seq * n_kv_heads * tiles:
-        raise KernelError("attention_decode_fused: too few counters")
-    if nsplit > 1 and (ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * nsplit * head_dim
-                       or ws_ml.numel() < n_seq * n_heads * nsplit * 2):
+    if not 1 <= nsplit <= 16:
+        raise KernelError(f"attention_decode_fused: {nsplit} splits, the merge takes 1 to 16")
+    if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * 4 * nsplit * head_dim \
+            or ws_ml.numel() < n_seq * n_heads * 4 * nsplit * 2:
         raise KernelError("attention_decode_fused: scratch too small for this batch and split count")
     lib = _attn_lib(head_dim)
     _check(lib, lib.dk_attn_decode_fused(_p(qkv), parts, n_parts, stride, _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin),
-                                         c_float(eps), _p(out), _p(ws_acc), _p(ws_ml), _p(counters), _p(k_store),
-                                         _p(v_store), _p(row_pos), _p(page_table), page_table.shape[1], n_seq, n_heads,
-                                         n_kv_heads, int(window or 0), c_float(scale), nsplit, int(bool(write_kv)),
-                                         _stream()), "attention_decode_fused")
+                                         c_float(eps), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store),
+                                         _p(row_pos), _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
+                                         int(window or 0), c_float(scale), nsplit, int(bool(write_kv)), _stream()),
+           "attention_decode_fused", 2)
 
 
 # ------------------------------------------------------------- tensor-core product for many rows

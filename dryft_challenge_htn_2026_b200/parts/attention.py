@@ -37,8 +37,9 @@ class GQAAttention(Part):
             raise ValueError("a position encoding that rewrites q and k itself (no fused tables) runs before the "
                              "per-head q/k norm; with qk_norm set that is not the order of this mixer")
         self.max_positions = 0
-        # decode in one launch (norm + rotation + cache write + attention + merge) instead of three;
-        # measured a few percent slower inside the full step on B200, so it is off by default
+        # decode attention that norms and rotates q and k itself and writes the cache (one launch
+        # fewer a layer); measured 1 to 5 percent slower inside the full step on B200: its blocks
+        # must wait for the projection's shared memory, which the small kernel between them hides
         self.fuse_decode = False
 
     def param_decls(self):
@@ -94,15 +95,12 @@ class GQAAttention(Part):
         window = s.window or 0
         o = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         if dtype == torch.bfloat16 and ctx.is_decode and self.fuse_decode:
-            # one kernel: q/k norm + rotation, cache write, attention over the cache, merge of the splits
+            # q/k norm + rotation and the cache write inside the attention kernel
             nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
             ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
                                         lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, dev))
-            counters = ctx.scratch(("attn_counters", ctx.n_seq, nkv, nh),
-                                   lambda: torch.zeros(ctx.n_seq * nkv * ((nh // nkv + 15) // 16), dtype=torch.int32,
-                                                       device=dev))
             api.attention_decode_fused(qkv, o, qn, kn, cos, sin, eps, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window,
-                                       s.scale, nsplit, ws_acc, ws_ml, counters, write_kv=writes)
+                                       s.scale, nsplit, ws_acc, ws_ml, write_kv=writes)
             return linear(o, self.w_o, ctx=ctx, allow_partial=True, residual=residual)
         q = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         api.qk_norm_rope_write(qkv, q, qn, kn, cos, sin, ctx.row_pos, ctx.row_seq, table, kv.k, kv.v, nh, nkv, hd, eps,

@@ -402,8 +402,8 @@ def test_gemv_stream(M, N, K):
                                                      (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 16)])
 @pytest.mark.parametrize("as_partial", [False, True])
 def test_attention_decode_fused(nh, nkv, hd, window, nsplit, as_partial):
-    """The one-launch decode mixer (norm + rotation + cache write + attention + merge) against the
-    separate kernels: same outputs, and the cache holds the new keys and values afterwards."""
+    """Decode attention that norms and rotates the new token's q and k itself and writes the cache,
+    against the separate kernels: same outputs, and the cache holds the same new keys and values."""
     before = [0, 63, 64, 300, 1000, 5]
     n = len(before)
     s = paged_setup(before, [1] * n, nkv, hd, torch.bfloat16, seed=60)
@@ -426,17 +426,16 @@ def test_attention_decode_fused(nh, nkv, hd, window, nsplit, as_partial):
     api.attention_generic(q, want, k_ref, v_ref, row_pos, row_seq, table, nh, nkv, hd, window, hd ** -0.5)
     out = torch.full_like(q, float("nan"))
     ws = api.attention_decode_ws(n + 1, nh, hd, nsplit, DEV)
-    counters = torch.zeros((n + 1) * nkv * ((nh // nkv + 15) // 16), dtype=torch.int32, device=DEV)
-    for _ in range(2):                                               # twice: the counters must come back to zero
+    for _ in range(2):                                               # twice: the second run finds its own writes
         api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh,
-                                   nkv, hd, window, hd ** -0.5, nsplit, *ws, counters)
+                                   nkv, hd, window, hd ** -0.5, nsplit, *ws)
         close(out[:n], want[:n], torch.bfloat16, "fused decode attention")
-        assert float(out[n:].float().abs().max()) == 0.0 and int(counters.abs().sum()) == 0
+        assert float(out[n:].float().abs().max()) == 0.0
     assert torch.equal(s["k_store"], k_ref) and torch.equal(s["v_store"], v_ref)
     # a layer that only reads another layer's cache: nothing is written
     k0 = s["k_store"].clone()
     api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd,
-                               window, hd ** -0.5, nsplit, *ws, counters, write_kv=False)
+                               window, hd ** -0.5, nsplit, *ws, write_kv=False)
     assert torch.equal(s["k_store"], k0)
     close(out[:n], want[:n], torch.bfloat16, "fused decode attention, read-only")
 

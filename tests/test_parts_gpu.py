@@ -148,7 +148,8 @@ def test_block_part(dtype):
 
 
 def test_attention_part_fused_decode_agrees_with_separate_kernels():
-    """The one-launch decode path of the attention part gives what the three-kernel path gives."""
+    """The decode path whose attention kernel norms, rotates and writes the cache itself gives what the
+    path with the separate kernel gives."""
     H, nh, nkv, hd = 64, 4, 2, 32
     spec = AttentionSpec(H, nh, nkv, hd, hd ** -0.5, RMSNormSpec(hd, 1e-6), RotaryHalfSpec(hd, 1e4), None)
     outs = []
