@@ -582,12 +582,15 @@ def gemm_tc_check():
         code = int(_tc_err.item())
         if code:
             _tc_err.zero_()
+            for t in _attn_sched.values():
+                t.zero_()
             raise KernelError(f"gemm_tc: a bounded wait ran out (code {code}); its results are not valid")
 
 
 # --------------------------------------------------------------- tensor-core prefill attention
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 TC_TILE_ROWS = 128
+_attn_sched = {}
 
 
 def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads, n_kv_heads, head_dim, window,
@@ -602,11 +605,15 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
         raise KernelError(f"attention_prefill_tc: head size {head_dim} (64 or 128) / heads {n_heads}:{n_kv_heads} not supported")
     if _tc_err is None:
         _tc_err = torch.zeros(1, dtype=torch.int32, device=q.device)
+    stream = torch.cuda.current_stream().cuda_stream
+    sched = _attn_sched.get(stream)          # the kernel's work counter: launches of one stream share it, in turn
+    if sched is None:
+        sched = _attn_sched[stream] = torch.zeros(2, dtype=torch.int32, device=q.device)
     lib = _lib("attention_tc.cu", {"HD": head_dim})
     _check(lib, lib.dk_attn_prefill_tc(_p(q), _p(out), _p(k_store), _p(v_store), c_longlong(q.shape[0]),
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
-                                       c_float(scale), _p(_tc_err), _stream()), "attention_prefill_tc")
+                                       c_float(scale), _p(_tc_err), _p(sched), _stream()), "attention_prefill_tc")
 
 
 def kernel_trace():

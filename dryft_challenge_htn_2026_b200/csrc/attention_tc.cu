@@ -19,6 +19,11 @@
 // K of the next block is fetched as soon as S has been computed, V as soon as P.V has: the loads
 // overlap the softmax and the other product. Two blocks fit on an SM (96 KB shared, 256 columns of
 // tensor memory each), so one block's softmax overlaps the other's mma.
+// The grid is persistent: two blocks an SM, each takes the next (tile, head) from a counter in
+// global memory until none is left. (With a block per tile the SMs did not take a new block while
+// one of their two was still running: the light tiles started only when a whole SM had drained,
+// and 40 % of the block slots stood empty.) The tiles come sorted by the keys they see, so the
+// heavy ones start first and the light ones fill the end.
 // Every mbarrier wait is bounded; a wait that runs out stores a code in *err, and the block still
 // frees its tensor memory and returns.
 #include <cuda.h>
@@ -32,8 +37,18 @@ static_assert(HD == 64 || HD == 128, "tensor-core prefill attention is built for
 
 #ifdef ATTN_TRACE
 __device__ long long g_trace[512];
-#define TRACE(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && i < 6) g_trace[(slot) + 16 * i] = clock64(); } while (0)
+#define TRACE(slot) do { if (blockIdx.x == 0 && items == 0 && i < 6) g_trace[(slot) + 16 * i] = clock64(); } while (0)
 DK_EXPORT int dk_attn_trace(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)); }
+// per block: start and end on the global timer (ns), SM, steps
+__device__ long long g_blocks[4 * 4096];
+__device__ long long g_clk[2 * 4096];
+DK_EXPORT int dk_attn_trace_clk(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_clk, sizeof(g_clk)); }
+DK_EXPORT int dk_attn_trace_blocks(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_blocks, sizeof(g_blocks)); }
+__device__ __forceinline__ long long trace_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #else
 #define TRACE(slot)
 #endif
@@ -135,47 +150,45 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// maximum of three, one instruction
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// grid (nh, tiles), 320 threads. tiles[2i] = sequence, tiles[2i+1] = first query (of 128) within
-// the sequence's chunk. q / out [T, nh*HD]; map_q over q as [T, nh*HD]; map_k / map_v over one
-// layer's K / V store as [pages * nkv * 64, HD].
+// grid min(items, 2 * SMs), 320 threads; item = tile * nh + head. tiles[2i] = sequence,
+// tiles[2i+1] = first query (of 128) within the sequence's chunk. q / out [T, nh*HD]; map_q over q
+// as [T, nh*HD]; map_k / map_v over one layer's K / V store as [pages * nkv * 64, HD].
+// sched[0]: next item, sched[1]: blocks that are done; both zero before the launch and after it.
 // Threads 0..255: softmax, two threads per query row (thread t and t+128 share row t & 127 and
 // take 64 of the 128 key columns each; warp w may read the tensor-memory lanes 32 (w % 4)..+31).
 // Warp 8, one thread: every tcgen05.mma. Warp 9, one thread: every TMA load.
+// The per-step barriers (K, V, S, P, O) complete once a step and bar_q once an item: their phases
+// run on over the items (step, items count what this block has done so far).
 __global__ void __launch_bounds__(320, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, bf16* out, const int* tiles, const int* cu_q,
+                       const __grid_constant__ CUtensorMap map_v, bf16* out, const int* tiles, int n_items, const int* cu_q,
                        const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
-                       int* err) {
+                       int* err, int* sched) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
     const uint32_t q_s = smem_u32(smem), k_s = q_s + Q_BYTES, v_s = k_s + KV_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + 2 * KV_BYTES);
     uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3, *bar_p = bars + 4, *bar_o = bars + 5;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 7);   // [0] the item all roles work on, [1] a wait ran out
     float* xch = reinterpret_cast<float*>(bars + 8);        // [2][256] row maxima / sums exchanged between the two threads of a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
-    // heads vary fastest: blocks start in launch order, so every head's heaviest tile (the tiles
-    // are sorted by the keys they see) starts before any light one, and the light ones fill the end
-    const int seq = tiles[2 * blockIdx.y], q0 = tiles[2 * blockIdx.y + 1];
-    const int h = blockIdx.x, kvh = h / (nh / nkv);
-    const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
-    const int rows_here = min(BM, q_len - q0);
-    const int flat0 = cu_q[seq] + q0;                      // first flat row of this tile
-    const int* pt = page_table + (size_t)seq * pt_stride;
-    const int max_pos = pos0 + q0 + rows_here - 1, min_pos = pos0 + q0;
-    const int blk_hi = max_pos / BN;
-    const int blk_lo = window > 0 ? max(0, min_pos - window + 1) / BN : 0;
-    const int n_blk = blk_hi - blk_lo + 1;
-
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1), mbar_init(bar_k, 1), mbar_init(bar_v, 1), mbar_init(bar_s, 1), mbar_init(bar_o, 1);
         mbar_init(bar_p, 256);
+        item_slot[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -189,6 +202,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t t_s = tmem, t_o = tmem + 128;           // S (and P over it) at columns 0..127, O at 128..128+HD
+
+    uint32_t step = 0, items = 0;                          // steps and items this block has finished
+    for (;;) {
+    if (threadIdx.x == 0) item_slot[0] = atomicAdd(&sched[0], 1);
+    __syncthreads();
+    const int item = item_slot[0];
+    if (item >= n_items || item_slot[1]) break;
+    const int seq = tiles[2 * (item / nh)], q0 = tiles[2 * (item / nh) + 1];
+    const int h = item % nh, kvh = h / (nh / nkv);
+    const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
+    const int rows_here = min(BM, q_len - q0);
+    const int flat0 = cu_q[seq] + q0;                      // first flat row of this tile
+    const int* pt = page_table + (size_t)seq * pt_stride;
+    const int max_pos = pos0 + q0 + rows_here - 1, min_pos = pos0 + q0;
+    const int blk_hi = max_pos / BN;
+    const int blk_lo = window > 0 ? max(0, min_pos - window + 1) / BN : 0;
+    const int n_blk = blk_hi - blk_lo + 1;
+#ifdef ATTN_TRACE
+    if (threadIdx.x == 0 && item < 4096) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_blocks[4 * item] = trace_now(), g_blocks[4 * item + 2] = smid, g_blocks[4 * item + 3] = n_blk, g_clk[2 * item] = clock64();
+    }
+#endif
 
     if (warp == 9) {
         if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
@@ -207,21 +244,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             load_kv(&map_k, k_s, blk_lo, bar_k);
             load_kv(&map_v, v_s, blk_lo, bar_v);
             for (int i = 0; i + 1 < n_blk; i++) {
-                if (!mbar_wait(bar_s, i & 1)) { atomicExch(err, 3); break; }   // S(i) is done with K
+                if (!mbar_wait(bar_s, (step + i) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }   // S(i) is done with K
                 load_kv(&map_k, k_s, blk_lo + i + 1, bar_k);
-                if (!mbar_wait(bar_o, i & 1)) { atomicExch(err, 3); break; }   // P.V(i) is done with V
+                if (!mbar_wait(bar_o, (step + i) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }   // P.V(i) is done with V
                 load_kv(&map_v, v_s, blk_lo + i + 1, bar_v);
             }
         }
     } else if (warp == 8) {
         if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
-            bool ok = mbar_wait(bar_q, 0);
+            bool ok = mbar_wait(bar_q, items & 1);
             for (int i = 0; i < n_blk && ok; i++) {
-                const uint32_t ph = i & 1;
+                const uint32_t ph = (step + i) & 1;
                 TRACE(0);
                 if (!mbar_wait(bar_k, ph)) { ok = false; break; }
                 TRACE(1);
-                if (i > 0 && !mbar_wait(bar_o, (i - 1) & 1)) { ok = false; break; }   // P (over S) has been consumed by P.V
+                if (i > 0 && !mbar_wait(bar_o, ph ^ 1)) { ok = false; break; }   // P (over S) has been consumed by P.V
                 fence_after();
 #pragma unroll
                 for (int hh = 0; hh < HALVES; hh++)
@@ -238,11 +275,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 fence_after();
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++)
-                    umma_ts(t_o, t_s + k * 8, desc_n_major(v_s + k * 16 * 128), IDESC_PV, (i | k) != 0);
+                    umma_ts(t_o, t_s + k * 8, desc_n_major(v_s + k * 16 * 128), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
                 umma_commit(bar_o);
                 TRACE(6);
             }
-            if (!ok) atomicExch(err, 1);
+            if (!ok) atomicExch(err, 1), item_slot[1] = 1;
         }
     } else {  // ------------------------------------------------------------------ softmax, two threads a row
         const int r = threadIdx.x & 127, half = threadIdx.x >> 7;   // row within the tile = tensor-memory lane; column half
@@ -254,7 +291,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
-            const uint32_t ph = i & 1;
+            const uint32_t ph = (step + i) & 1;
             const int key0 = (blk_lo + i) * BN + col0;
             if (threadIdx.x == 0) TRACE(8);
             if (!mbar_wait(bar_s, ph)) { ok = false; break; }
@@ -272,7 +309,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                 for (int c = 0; c < 2; c++)
 #pragma unroll
-                    for (int j = 0; j < 32; j++) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(v[c][j]));
+                    for (int j = 0; j < 32; j += 2)
+                        mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[c][j]), __uint_as_float(v[c][j + 1]));
             } else {
 #pragma unroll
                 for (int c = 0; c < 2; c++)
@@ -295,12 +333,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // float32 / bfloat16 range, the final O / l is the same, and O need not be rescaled
             if (m != -INFINITY && m_new - m < 8.f) m_new = m;
             const float ms = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = ex2(m - ms);
-            // O of the earlier blocks is rescaled when the reference moved (P.V of the last block must be complete);
-            // each thread of a row takes half of the columns of O
+            const float alpha = m_new == m ? 1.f : ex2(m - ms);
+            // O of the earlier blocks is rescaled when the reference moved. P.V of the last block is complete: S of this
+            // block was issued after it, and the arrival on bar_s covers every tcgen05 operation issued before it.
+            // Each thread of a row takes half of the columns of O.
             if (i > 0) {
-                if (!mbar_wait(bar_o, (i - 1) & 1)) { ok = false; break; }
-                fence_after();
                 if (__any_sync(0xffffffffu, alpha != 1.f)) {   // tcgen05.ld/st are warp-wide: all lanes or none
 #pragma unroll 1
                     for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
@@ -336,7 +373,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(bar_p);
             if (threadIdx.x == 0) TRACE(13);
         }
-        if (ok && n_blk > 0) ok = mbar_wait(bar_o, (n_blk - 1) & 1);
+        if (ok) ok = mbar_wait(bar_o, (step + n_blk - 1) & 1);
         // the row's sum is over both threads of the row
         xch[threadIdx.x] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
@@ -363,12 +400,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         } else if (lane == 0) {
-            atomicExch(err, 2);
+            atomicExch(err, 2), item_slot[1] = 1;
         }
     }
+    // everyone is done with the item: O has been read out of tensor memory, the item slot is free
+    step += n_blk, items++;
     fence_before();
     __syncthreads();
+    fence_after();
+#ifdef ATTN_TRACE
+    if (threadIdx.x == 0 && item < 4096) g_blocks[4 * item + 1] = trace_now(), g_clk[2 * item + 1] = clock64();
+#endif
+    }
     pdl_launch_dependents();
+    if (threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) sched[0] = 0, sched[1] = 0;   // the last block leaves zeros for the next launch
     if (warp == 8) {
         fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
@@ -410,12 +455,13 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 DK_EXPORT int dk_attn_tc_head_dim() { return HD; }
 
 // q, out [n_tok, nh*HD] bf16; k_store, v_store [n_pages, nkv, 64, HD] bf16; tiles [n_tiles][2] =
-// (sequence, first query of a 128-row tile within its chunk); err: device int for a wait that ran out.
+// (sequence, first query of a 128-row tile within its chunk); err: device int for a wait that ran out;
+// sched: two device ints, zero (the kernel leaves them zero), not shared with a launch on another stream.
 DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, const void* v_store, long long n_tok,
                                  long long n_pages, const int* tiles, int n_tiles, const int* cu_q, const int* seq_pos0,
                                  const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
-                                 cudaStream_t st) {
-    if (nh % nkv != 0 || err == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
+                                 int* sched, cudaStream_t st) {
+    if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
     constexpr size_t smem = 1024 + Q_BYTES + 2 * KV_BYTES + 8 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
     static bool attr = false;
     if (!attr) {
@@ -428,6 +474,12 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
     if (!e) e = make_map(&mk, k_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
     if (!e) e = make_map(&mv, v_store, n_pages * nkv * DK_PAGE, HD, DK_PAGE);
     if (e) return e;
-    return dk_launch(attn_prefill_tc_kernel, dim3(nh, n_tiles), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, cu_q,
-                     seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err);
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long n_items = (long long)n_tiles * nh;
+    if (n_items > 0x7fffffffLL - 4 * sms) return (int)cudaErrorInvalidValue;
+    const int blocks = (int)(n_items < 2LL * sms ? n_items : 2LL * sms);
+    return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
+                     cu_q, seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err, sched);
 }
