@@ -55,10 +55,12 @@ __device__ __forceinline__ long long trace_now() {
 
 namespace {
 
-constexpr int BM = 128, BN = 128;                 // queries per block, keys per step
+constexpr int BM = 128, BN = 64;                  // queries per block, keys per step (one cache page)
+static_assert(BN == DK_PAGE, "a step is one page of the cache");
 constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms across the head
-constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;
-constexpr int ATOM_ROWS_BYTES = 128 * 128;        // 128 rows of one 64-column atom
+constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;   // Q tile; one stage of K or of V
+constexpr int Q_ATOM_BYTES = BM * 128;            // the 128 query rows of one 64-column atom
+constexpr int KV_ATOM_BYTES = BN * 128;           // the 64 key rows of one 64-column atom
 constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -97,9 +99,9 @@ __device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
            ((uint64_t)2 << 61);
 }
 // N-major operand (V: keys are the rows in shared memory, the head columns are contiguous),
-// 128-byte swizzle: the next 64 columns are ATOM_ROWS_BYTES away, the next 8 keys 1024 bytes.
+// 128-byte swizzle: the next 64 columns are KV_ATOM_BYTES away, the next 8 keys 1024 bytes.
 __device__ __forceinline__ uint64_t desc_n_major(uint32_t addr) {
-    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(ATOM_ROWS_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(KV_ATOM_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 __device__ __forceinline__ void umma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
@@ -176,18 +178,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        int* err, int* sched) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);
-    const uint32_t q_s = smem_u32(smem), k_s = q_s + Q_BYTES, v_s = k_s + KV_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + 2 * KV_BYTES);
-    uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_s = bars + 3, *bar_p = bars + 4, *bar_o = bars + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
-    volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 7);   // [0] the item all roles work on, [1] a wait ran out
-    float* xch = reinterpret_cast<float*>(bars + 8);        // [2][256] row maxima / sums exchanged between the two threads of a row
+    const uint32_t q_s = smem_u32(smem), k_s = q_s + Q_BYTES, v_s = k_s + 2 * KV_BYTES;   // Q, K stages 0 1, V stages 0 1
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q_BYTES + 4 * KV_BYTES);
+    // one barrier per stage / buffer: step t (counted over all items of the block) uses number t & 1
+    uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 7, *bar_o = bars + 9;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 12);  // [0] the item all roles work on, [1] a wait ran out
+    float* xch = reinterpret_cast<float*>(bars + 13);       // [2][256] row maxima / sums exchanged between the two threads of a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
     if (threadIdx.x == 0) {
-        mbar_init(bar_q, 1), mbar_init(bar_k, 1), mbar_init(bar_v, 1), mbar_init(bar_s, 1), mbar_init(bar_o, 1);
-        mbar_init(bar_p, 256);
+        mbar_init(bar_q, 1);
+        for (int b = 0; b < 2; b++)
+            mbar_init(bar_k + b, 1), mbar_init(bar_v + b, 1), mbar_init(bar_s + b, 1), mbar_init(bar_o + b, 1), mbar_init(bar_p + b, 256);
         item_slot[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -201,14 +205,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_s = tmem, t_o = tmem + 128;           // S (and P over it) at columns 0..127, O at 128..128+HD
+    const uint32_t t_s = tmem, t_o = tmem + 128;           // S buffers (and P over them) at columns 0..63 and 64..127, O at 128..128+HD
 
     uint32_t step = 0, items = 0;                          // steps and items this block has finished
+    int next_item = threadIdx.x == 0 ? atomicAdd(&sched[0], 1) : 0;
     for (;;) {
-    if (threadIdx.x == 0) item_slot[0] = atomicAdd(&sched[0], 1);
+    if (threadIdx.x == 0) item_slot[0] = next_item;
     __syncthreads();
     const int item = item_slot[0];
     if (item >= n_items || item_slot[1]) break;
+    if (threadIdx.x == 0) next_item = atomicAdd(&sched[0], 1);   // the one after: the answer is not needed before this item is done
     const int seq = tiles[2 * (item / nh)], q0 = tiles[2 * (item / nh) + 1];
     const int h = item % nh, kvh = h / (nh / nkv);
     const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
@@ -227,56 +233,80 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 #endif
 
+    // Step j of the item is step t = step + j of the block; it uses stage / buffer / barrier t & 1, whose
+    // barriers are then in their phase (t >> 1) & 1.
     if (warp == 9) {
         if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
-            auto load_kv = [&](const CUtensorMap* map, uint32_t dst, int blk, uint64_t* bar) {
-                mbar_expect_tx(bar, KV_BYTES);
-                for (int pg = 0; pg < 2; pg++) {
-                    int page = pt[min(2 * blk + pg, pt_stride - 1)];
-                    if (page < 0) page = 0;                 // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
-                    const int row = (page * nkv + kvh) * DK_PAGE;
-                    for (int hh = 0; hh < HALVES; hh++)
-                        tma_load_2d(dst + hh * ATOM_ROWS_BYTES + pg * (DK_PAGE * 128), map, hh * 64, row, bar);
-                }
+            auto load_kv = [&](const CUtensorMap* map, uint32_t stages, uint64_t* bar, int j) {
+                const uint32_t b = (step + j) & 1;
+                mbar_expect_tx(bar + b, KV_BYTES);
+                int page = pt[min(blk_lo + j, pt_stride - 1)];
+                if (page < 0) page = 0;                     // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
+                const int row = (page * nkv + kvh) * DK_PAGE;
+                for (int hh = 0; hh < HALVES; hh++)
+                    tma_load_2d(stages + b * KV_BYTES + hh * KV_ATOM_BYTES, map, hh * 64, row, bar + b);
             };
             mbar_expect_tx(bar_q, Q_BYTES);
-            for (int hh = 0; hh < HALVES; hh++) tma_load_2d(q_s + hh * ATOM_ROWS_BYTES, &map_q, h * HD + hh * 64, flat0, bar_q);
-            load_kv(&map_k, k_s, blk_lo, bar_k);
-            load_kv(&map_v, v_s, blk_lo, bar_v);
-            for (int i = 0; i + 1 < n_blk; i++) {
-                if (!mbar_wait(bar_s, (step + i) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }   // S(i) is done with K
-                load_kv(&map_k, k_s, blk_lo + i + 1, bar_k);
-                if (!mbar_wait(bar_o, (step + i) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }   // P.V(i) is done with V
-                load_kv(&map_v, v_s, blk_lo + i + 1, bar_v);
+            for (int hh = 0; hh < HALVES; hh++) tma_load_2d(q_s + hh * Q_ATOM_BYTES, &map_q, h * HD + hh * 64, flat0, bar_q);
+            load_kv(&map_k, k_s, bar_k, 0);
+            load_kv(&map_v, v_s, bar_v, 0);
+            if (n_blk > 1) load_kv(&map_k, k_s, bar_k, 1), load_kv(&map_v, v_s, bar_v, 1);
+            // in the order in which the stages come free: S(j) is done with K(j), then P.V(j-1) with V(j-1)
+            for (int j = 0; j + 2 < n_blk; j++) {
+                const uint32_t t = step + j;
+                if (!mbar_wait(bar_s + (t & 1), (t >> 1) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }
+                load_kv(&map_k, k_s, bar_k, j + 2);
+                if (j >= 1) {
+                    if (!mbar_wait(bar_o + ((t - 1) & 1), ((t - 1) >> 1) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }
+                    load_kv(&map_v, v_s, bar_v, j + 1);
+                }
+            }
+            if (n_blk > 2) {                                // the last value page: after P.V(n - 3)
+                const uint32_t t = step + n_blk - 3;
+                if (mbar_wait(bar_o + (t & 1), (t >> 1) & 1)) load_kv(&map_v, v_s, bar_v, n_blk - 1);
+                else atomicExch(err, 3), item_slot[1] = 1;
             }
         }
     } else if (warp == 8) {
         if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
-            bool ok = mbar_wait(bar_q, items & 1);
-            for (int i = 0; i < n_blk && ok; i++) {
-                const uint32_t ph = (step + i) & 1;
-                TRACE(0);
-                if (!mbar_wait(bar_k, ph)) { ok = false; break; }
-                TRACE(1);
-                if (i > 0 && !mbar_wait(bar_o, ph ^ 1)) { ok = false; break; }   // P (over S) has been consumed by P.V
-                fence_after();
+            // S(j) = Q . K(j)^T into buffer (step + j) & 1
+            auto issue_s = [&](int j) {
+                const uint32_t b = (step + j) & 1;
 #pragma unroll
                 for (int hh = 0; hh < HALVES; hh++)
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        umma_ss(t_s, desc_k_major(q_s + hh * ATOM_ROWS_BYTES + k * 32), desc_k_major(k_s + hh * ATOM_ROWS_BYTES + k * 32),
-                                IDESC_S, (hh | k) != 0);
-                umma_commit(bar_s);
-                TRACE(2);
-                if (!mbar_wait(bar_p, ph)) { ok = false; break; }
+                        umma_ss(t_s + b * BN, desc_k_major(q_s + hh * Q_ATOM_BYTES + k * 32),
+                                desc_k_major(k_s + b * KV_BYTES + hh * KV_ATOM_BYTES + k * 32), IDESC_S, (hh | k) != 0);
+                umma_commit(bar_s + b);
+            };
+            bool ok = mbar_wait(bar_q, items & 1) && mbar_wait(bar_k + (step & 1), (step >> 1) & 1);
+            if (ok) {
+                fence_after();
+                issue_s(0);
+            }
+            for (int i = 0; i < n_blk && ok; i++) {
+                const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
+                TRACE(0);
+                if (i + 1 < n_blk) {                        // S of the next step, while the softmax warps work on this one
+                    const uint32_t tn = t + 1;
+                    if (!mbar_wait(bar_k + (tn & 1), (tn >> 1) & 1)) { ok = false; break; }
+                    TRACE(1);
+                    // its buffer held P of the step before this one: P.V of that step must be done with it
+                    if (i >= 1 && !mbar_wait(bar_o + (tn & 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
+                    fence_after();
+                    issue_s(i + 1);
+                    TRACE(2);
+                }
+                if (!mbar_wait(bar_p + b, ph)) { ok = false; break; }
                 TRACE(4);
-                if (!mbar_wait(bar_v, ph)) { ok = false; break; }   // P is written, V is here
+                if (!mbar_wait(bar_v + b, ph)) { ok = false; break; }   // P is written, V is here
                 TRACE(5);
                 fence_after();
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++)
-                    umma_ts(t_o, t_s + k * 8, desc_n_major(v_s + k * 16 * 128), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
-                umma_commit(bar_o);
+                    umma_ts(t_o, t_s + b * BN + k * 8, desc_n_major(v_s + b * KV_BYTES + k * 16 * 128), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
+                umma_commit(bar_o + b);
                 TRACE(6);
             }
             if (!ok) atomicExch(err, 1), item_slot[1] = 1;
@@ -287,43 +317,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int qpos = pos0 + q0 + r;
         const int key_lo = window > 0 ? max(0, qpos - window + 1) : 0;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const int col0 = half * 64;                          // this thread's key columns within a block
+        const int col0 = half * (BN / 2);                    // this thread's key columns within a step
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
-            const uint32_t ph = (step + i) & 1;
+            const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
             const int key0 = (blk_lo + i) * BN + col0;
             if (threadIdx.x == 0) TRACE(8);
-            if (!mbar_wait(bar_s, ph)) { ok = false; break; }
+            if (!mbar_wait(bar_s + b, ph)) { ok = false; break; }
             if (threadIdx.x == 0) TRACE(9);
             fence_after();
-            uint32_t v[2][32];
-            tmem_ld32(t_s + lane_off + col0, v[0]);
-            tmem_ld32(t_s + lane_off + col0 + 32, v[1]);
+            uint32_t v[32];
+            tmem_ld32(t_s + lane_off + b * BN + col0, v);
             tmem_wait_ld();
             if (threadIdx.x == 0) TRACE(10);
-            // every key of the block visible to every row of the tile: no per-element test
+            // every key of the step visible to every row of the tile: no per-element test
             const bool open = window <= 0 && (blk_lo + i) * BN + BN - 1 <= min_pos;
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (open) {
 #pragma unroll
-                for (int c = 0; c < 2; c++)
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2)
-                        mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[c][j]), __uint_as_float(v[c][j + 1]));
+                for (int j = 0; j < 32; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
             } else {
 #pragma unroll
-                for (int c = 0; c < 2; c++)
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int key = key0 + c * 32 + j;
-                        const float sc = (valid && key <= qpos && key >= key_lo) ? __uint_as_float(v[c][j]) : -INFINITY;
-                        v[c][j] = __float_as_uint(sc);
-                        mx4[j & 3] = fmaxf(mx4[j & 3], sc);
-                    }
+                for (int j = 0; j < 32; j++) {
+                    const int key = key0 + j;
+                    const float sc = (valid && key <= qpos && key >= key_lo) ? __uint_as_float(v[j]) : -INFINITY;
+                    v[j] = __float_as_uint(sc);
+                    mx4[j & 3] = fmaxf(mx4[j & 3], sc);
+                }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // sl2 > 0: scaling keeps the order
-            // the row's maximum is over both threads of the row
+            // the row's maximum is over both threads of the row; once both have been here, both have read their S
+            // (P of one goes over columns of S that the other reads)
             xch[(i & 1) * 256 + threadIdx.x] = mx;
             if (threadIdx.x == 0) TRACE(7);
             asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
@@ -334,46 +359,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (m != -INFINITY && m_new - m < 8.f) m_new = m;
             const float ms = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = m_new == m ? 1.f : ex2(m - ms);
-            // O of the earlier blocks is rescaled when the reference moved. P.V of the last block is complete: S of this
-            // block was issued after it, and the arrival on bar_s covers every tcgen05 operation issued before it.
-            // Each thread of a row takes half of the columns of O.
-            if (i > 0) {
-                if (__any_sync(0xffffffffu, alpha != 1.f)) {   // tcgen05.ld/st are warp-wide: all lanes or none
+            // O of the earlier steps is rescaled when the reference moved, once P.V of the last step is complete
+            // (that of the steps before it then is too). Each thread of a row takes half of the columns of O.
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // tcgen05.ld/st are warp-wide: all lanes or none
+                if (!mbar_wait(bar_o + (b ^ 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
+                fence_after();
 #pragma unroll 1
-                    for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(t_o + lane_off + c, o);
-                        tmem_wait_ld();
+                for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(t_o + lane_off + c, o);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                        tmem_st32(t_o + lane_off + c, o);
-                    }
+                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                    tmem_st32(t_o + lane_off + c, o);
                 }
             }
             if (threadIdx.x == 0) TRACE(11);
-            // P = exp2(S * sl2 - m), its sum, and P as bfloat16 over the columns of S
+            // P = exp2(S * sl2 - m), its sum, and P as bfloat16 over the first columns of this S buffer
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t p[16];
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t p[16];
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const float e0 = ex2(fmaf(__uint_as_float(v[c][j]), sl2, -ms)), e1 = ex2(fmaf(__uint_as_float(v[c][j + 1]), sl2, -ms));
-                    sum4[(j >> 1) & 3] += e0 + e1;
-                    __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
-                    p[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
-                }
-                tmem_st16(t_s + lane_off + (col0 + c * 32) / 2, p);
+            for (int j = 0; j < 32; j += 2) {
+                const float e0 = ex2(fmaf(__uint_as_float(v[j]), sl2, -ms)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sl2, -ms));
+                sum4[(j >> 1) & 3] += e0 + e1;
+                __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
+                p[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
+            tmem_st16(t_s + lane_off + b * BN + col0 / 2, p);
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m = m_new;
             if (threadIdx.x == 0) TRACE(12);
             tmem_wait_st();
             fence_before();
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p + b);
             if (threadIdx.x == 0) TRACE(13);
         }
-        if (ok) ok = mbar_wait(bar_o, (step + n_blk - 1) & 1);
+        if (ok) ok = mbar_wait(bar_o + ((step + n_blk - 1) & 1), ((step + n_blk - 1) >> 1) & 1);
         // the row's sum is over both threads of the row
         xch[threadIdx.x] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
@@ -462,7 +483,7 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
                                  const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
                                  int* sched, cudaStream_t st) {
     if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
-    constexpr size_t smem = 1024 + Q_BYTES + 2 * KV_BYTES + 8 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 13 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -435,17 +435,23 @@ __global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, con
     if (!on || is_v) return;
     const float* nw = hidx < nh ? qn : kn;
     const float rs = nw ? rsqrtf(ss / (float)hd + eps) : 1.f;
+    // weights and angles of this lane's 8 + 8 elements: 16-byte loads (hd % 16 == 0 keeps them aligned)
+    float w1[8], w2[8], cs[8], sn[8];
+    auto load8 = [](const float* p, float (&f)[8]) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+    };
+    if (nw) load8(nw + 8 * j, w1), load8(nw + half + 8 * j, w2);
+    if (cos_t) load8(cos_t + (size_t)pos * half + 8 * j, cs), load8(sin_t + (size_t)pos * half + 8 * j, sn);
     float o1[8], o2[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const int d = 8 * j + i;
         float a1 = x1[i] * rs, a2 = x2[i] * rs;
-        if (nw) a1 *= nw[d], a2 *= nw[d + half];
+        if (nw) a1 *= w1[i], a2 *= w2[i];
         o1[i] = a1, o2[i] = a2;
         if (cos_t) {
-            const float c = cos_t[(size_t)pos * half + d], s = sin_t[(size_t)pos * half + d];
-            o1[i] = a1 * c - a2 * s;
-            o2[i] = a2 * c + a1 * s;
+            o1[i] = a1 * cs[i] - a2 * sn[i];
+            o2[i] = a2 * cs[i] + a1 * sn[i];
         }
     }
     reinterpret_cast<uint4*>(dst)[j] = pack8(o1);
