@@ -541,6 +541,37 @@ def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
     return Partial(ws) if sk > 1 else out
 
 
+TC_QKV_HEAD_DIMS = (64, 128)
+
+
+def gemm_tc_qkv(x, w, q_out, q_norm_w, k_norm_w, cos, sin, eps, row_pos, row_seq, page_table, k_store, v_store, n_heads,
+                n_kv_heads, head_dim, write_kv=True):
+    """The fused q/k/v projection x . [Wq; Wk; Wv]^T of a prefill step with ``qk_norm_rope_write``
+    in the epilogue of the tensor-core product: the float32 accumulator rows go through the per-head
+    norm and the rotation, q to ``q_out``, k and v into the paged cache; the projection itself is
+    never written. Head sizes 64 and 128; arguments as ``qk_norm_rope_write``."""
+    global _tc_err
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(q_out, "q_out", torch.bfloat16, 2)
+    _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
+    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
+    _need(row_pos, "row_pos", torch.int32, 1), _need(row_seq, "row_seq", torch.int32, 1)
+    _need(page_table, "page_table", torch.int32, 2), _need(k_store, "k_store", torch.bfloat16), _need(v_store, "v_store", torch.bfloat16)
+    M, K = x.shape
+    if head_dim not in TC_QKV_HEAD_DIMS or K % 8 or tuple(w.shape) != ((n_heads + 2 * n_kv_heads) * head_dim, K) \
+            or tuple(q_out.shape) != (M, n_heads * head_dim) or row_pos.numel() < M or row_seq.numel() < M:
+        raise KernelError(f"gemm_tc_qkv: x{tuple(x.shape)} w{tuple(w.shape)} heads {n_heads}:{n_kv_heads} of {head_dim} "
+                          "not supported (head size 64 or 128, K % 8 == 0)")
+    if cos is not None and (cos.shape[1] != head_dim // 2 or sin.shape != cos.shape):
+        raise KernelError("gemm_tc_qkv: angle tables must be [positions, head_dim / 2]")
+    if _tc_err is None:
+        _tc_err = torch.zeros(1, dtype=torch.int32, device=x.device)
+    lib = _lib("gemm_tc.cu")
+    _check(lib, lib.dk_gemm_tc_qkv(_p(x), _p(w), M, K, _p(_tc_err), _p(q_out), _p(k_store), _p(v_store), _p(q_norm_w),
+                                   _p(k_norm_w), _p(cos), _p(sin), _p(row_pos), _p(row_seq), _p(page_table),
+                                   page_table.shape[1], n_heads, n_kv_heads, head_dim, c_float(eps), int(bool(write_kv)),
+                                   _stream()), "gemm_tc_qkv")
+
+
 TC_SKINNY_MAX_ROWS = 128
 
 

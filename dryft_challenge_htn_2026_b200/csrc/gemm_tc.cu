@@ -1,6 +1,8 @@
 // The prefill matrix product on the 5th-generation tensor cores:
 //   out[M,N] = x[M,K] . W[N,K]^T                         (mode 0, bfloat16 out)
 //   out[M,N] = silu(x . Wgate^T) * (x . Wup^T)           (mode 2, W = [gate; up], N rows each)
+//   q, K cache, V cache <- x . [Wq; Wk; Wv]^T             (modes 3, 4: per-head RMSNorm and rotation of
+//                          q and k in the epilogue, q to its tensor, k and v into the paged cache)
 // float32 accumulation in tensor memory. Reference: the reference engine hands these products to
 // the library (engine/fused.py:993-995) and runs SiLU*up as a separate kernel (:175-188); here the
 // gated product writes silu(gate)*up directly, so the [M, 2N] intermediate never exists.
@@ -89,6 +91,128 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// What the epilogue of modes 3 and 4 needs beside the product: the fused projection's columns are heads of
+// hd (64 or 128) columns, nh of q, then nkv of k, then nkv of v. The float32 accumulator row of a
+// token goes through the per-head RMSNorm (weights qn / kn, may be null) and the rotate-half
+// rotation by the angles at its position (tables [positions][hd/2], may be null) exactly as in
+// qk_norm_rope_write, without the rounding to bfloat16 in between; q goes to q_out [M, nh*hd], k
+// and v to the token's place in the paged cache (not when write_kv == 0). Rows with position < 0
+// are padding: nothing is stored for them.
+struct QkvEpilogue {
+    bf16 *q_out, *k_store, *v_store;
+    const float *qn, *kn, *cos_t, *sin_t;
+    const int *row_pos, *row_seq, *page_table;
+    int pt_stride, nh, nkv, hd, write_kv;
+    float eps;
+};
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void load16(const float* p, float (&f)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(p + i);
+        f[i] = v.x, f[i + 1] = v.y, f[i + 2] = v.z, f[i + 3] = v.w;
+    }
+}
+__device__ __forceinline__ void store16(bf16* p, const float (&f)[16]) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 8) {
+        uint4 pk;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int j = 0; j < 4; j++) q[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
+        *reinterpret_cast<uint4*>(p + i) = pk;
+    }
+}
+
+// The epilogue of modes 3 (hd 128) and 4 (hd 64) for one accumulator row: columns [n0, n0 + BN) of
+// the projection, BN / HDT heads. Every tcgen05.ld is executed by the whole warp; only the stores
+// depend on the lane's row. First the scale of every head's norm, then the head in pieces of 16
+// columns and their partners half a head further: a piece's angles serve all heads of the tile, and
+// those of the next piece are requested before this one is worked on (with four warps an SM nothing
+// else hides the latency of a load).
+template <int BN, int HDT>
+__device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& qe, uint32_t acc, int row, int M, int n0, int N) {
+    constexpr int HALF = HDT / 2, HEADS = BN / HDT;
+    const int pos = row < M ? qe.row_pos[row] : -1;
+    const float* cos_r = qe.cos_t ? qe.cos_t + (size_t)max(pos, 0) * HALF : nullptr;
+    const float* sin_r = qe.cos_t ? qe.sin_t + (size_t)max(pos, 0) * HALF : nullptr;
+    float cs[2][16], sn[2][16];
+    if (cos_r) load16(cos_r, cs[0]), load16(sin_r, sn[0]);
+    int page = 0;
+    if (pos >= 0 && qe.write_kv) page = qe.page_table[(size_t)qe.row_seq[row] * qe.pt_stride + pos / DK_PAGE];
+    float rs[HEADS];
+    bf16* dst[HEADS];
+#pragma unroll
+    for (int hi = 0; hi < HEADS; hi++) {
+        const int head = (n0 + hi * HDT) / HDT;
+        const bool there = n0 + hi * HDT < N, is_q = head < qe.nh, is_v = head >= qe.nh + qe.nkv;
+        dst[hi] = nullptr;
+        rs[hi] = 1.f;
+        if (!there) continue;
+        if (pos >= 0 && (is_q || qe.write_kv))
+            dst[hi] = is_q ? qe.q_out + ((size_t)row * qe.nh + head) * HDT
+                           : (is_v ? qe.v_store : qe.k_store) + kv_offset(page, qe.nkv, (head - qe.nh) % qe.nkv, pos % DK_PAGE, HDT);
+        if (!is_v && (is_q ? qe.qn : qe.kn) != nullptr) {
+            float ss = 0.f;
+#pragma unroll
+            for (int c = 0; c < HDT; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(acc + hi * HDT + c, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) ss += __uint_as_float(v[i]) * __uint_as_float(v[i]);
+            }
+            rs[hi] = rsqrtf(ss / (float)HDT + qe.eps);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < HALF; c += 16) {
+        const int cur = (c / 16) & 1;
+        if (cos_r && c + 16 < HALF) load16(cos_r + c + 16, cs[cur ^ 1]), load16(sin_r + c + 16, sn[cur ^ 1]);
+#pragma unroll
+        for (int hi = 0; hi < HEADS; hi++) {
+            const int head = (n0 + hi * HDT) / HDT;
+            if (n0 + hi * HDT >= N) continue;
+            const bool is_q = head < qe.nh, is_v = head >= qe.nh + qe.nkv;
+            uint32_t a[16], b[16];
+            tmem_ld16(acc + hi * HDT + c, a);
+            tmem_ld16(acc + hi * HDT + HALF + c, b);
+            if (dst[hi] == nullptr) continue;
+            float x1[16], x2[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) x1[i] = __uint_as_float(a[i]), x2[i] = __uint_as_float(b[i]);
+            if (!is_v) {
+                const float* nw = is_q ? qe.qn : qe.kn;
+                if (nw) {
+                    float w[16];
+                    load16(nw + c, w);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) x1[i] = x1[i] * rs[hi] * w[i];
+                    load16(nw + HALF + c, w);
+#pragma unroll
+                    for (int i = 0; i < 16; i++) x2[i] = x2[i] * rs[hi] * w[i];
+                }
+                if (cos_r) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const float o1 = x1[i] * cs[cur][i] - x2[i] * sn[cur][i], o2 = x2[i] * cs[cur][i] + x1[i] * sn[cur][i];
+                        x1[i] = o1, x2[i] = o2;
+                    }
+                }
+            }
+            store16(dst[hi] + c, x1);
+            store16(dst[hi] + HALF + c, x2);
+        }
+    }
+}
+
 // MODE 0: W tile rows [n0, n0+BN). MODE 2 (BN = 256): rows [n0, n0+128) of gate at accumulator
 // columns 0..127 and the same rows of up (row offset N) at columns 128..255; n0 counts outputs.
 // Persistent: block b computes tiles b, b + gridDim.x, ... (row tiles fastest, so the blocks that
@@ -97,7 +221,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 template <int BN, int MODE>
 __global__ void __launch_bounds__(192)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, bf16* out, int M,
-               int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws, int STAGES, int a_bytes) {
+               int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws, int STAGES, int a_bytes,
+               const __grid_constant__ QkvEpilogue qe) {
     constexpr int B_BYTES = BN * BK * 2;
     // Shared memory: STAGES weight tiles, then STAGES tiles of x a_bytes apart, then the barriers.
     // a_bytes = rows of x that are really loaded x 128 bytes. The mma always reads 128 rows (A_BYTES)
@@ -234,8 +359,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + buf * BN + ((uint32_t)(q * 32) << 16);
+            if (MODE == 3) qkv_epilogue_row<BN, 128>(qe, acc, row, M, n0, N);
+            if (MODE == 4) qkv_epilogue_row<BN, 64>(qe, acc, row, M, n0, N);
 #pragma unroll 1
-            for (int c = 0; c < OUT_COLS; c += 32) {
+            for (int c = 0; c < (MODE >= 3 ? 0 : OUT_COLS); c += 32) {
                 uint32_t v[32];
                 tmem_ld32(acc + c, v);
                 float f[32];
@@ -326,7 +453,8 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }
 
 template <int BN, int MODE>
-int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, int SK, float* ws, cudaStream_t st) {
+int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* err, int SK, float* ws, cudaStream_t st,
+           const QkvEpilogue& qe = QkvEpilogue{}) {
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;
     constexpr int B_BYTES = BN * BK * 2;
     // rows of x a TMA box loads: all 128 of a tile, or for a single tile of few rows (a decode step)
@@ -354,7 +482,7 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(units < sms ? units : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
-                     m_tiles, tiles, err, SK, ws, stages, a_bytes);
+                     m_tiles, tiles, err, SK, ws, stages, a_bytes, qe);
 }
 
 }  // namespace
@@ -380,4 +508,23 @@ DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, 
     if (mode == 0 && bn == 128) return launch<128, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
     if (mode == 0) return launch<256, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
     return (int)cudaErrorInvalidValue;
+}
+
+// The fused q/k/v projection of a prefill step with the work of qk_norm_rope_write in its epilogue
+// (see QkvEpilogue): x [M,K] bf16, W [(nh + 2 nkv) * hd, K] bf16 = [Wq; Wk; Wv], hd 64 or 128;
+// q_out [M, nh*hd] bf16; k_store, v_store [pages, nkv, 64, hd] bf16; qn, kn [hd] or null; cos_t,
+// sin_t [positions, hd/2] or null; row_pos, row_seq [M]; page_table [sequences, pt_stride].
+DK_EXPORT int dk_gemm_tc_qkv(const void* x, const void* W, int M, int K, int* err, void* q_out, void* k_store, void* v_store,
+                             const float* qn, const float* kn, const float* cos_t, const float* sin_t, const int* row_pos,
+                             const int* row_seq, const int* page_table, int pt_stride, int nh, int nkv, int hd, float eps,
+                             int write_kv, cudaStream_t st) {
+    if (M < 1 || K < 8 || K % 8 != 0 || err == nullptr || (hd != 64 && hd != 128) || nh < 1 || nkv < 1)
+        return (int)cudaErrorInvalidValue;
+    if (((uintptr_t)x | (uintptr_t)W | (uintptr_t)q_out | (uintptr_t)k_store | (uintptr_t)v_store | (uintptr_t)qn |
+         (uintptr_t)kn | (uintptr_t)cos_t | (uintptr_t)sin_t) % 16 != 0)
+        return (int)cudaErrorInvalidValue;
+    QkvEpilogue qe{(bf16*)q_out, (bf16*)k_store, (bf16*)v_store, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table,
+                   pt_stride, nh, nkv, hd, write_kv, eps};
+    if (hd == 128) return launch<256, 3>((const bf16*)x, (const bf16*)W, nullptr, M, (nh + 2 * nkv) * hd, K, err, 1, nullptr, st, qe);
+    return launch<256, 4>((const bf16*)x, (const bf16*)W, nullptr, M, (nh + 2 * nkv) * hd, K, err, 1, nullptr, st, qe);
 }

@@ -1,6 +1,7 @@
 """Causal grouped-query attention mixer over the paged key/value cache.
 
-forward = fused q/k/v projection -> per-head q/k norm + rotary + cache write (one kernel) ->
+forward = fused q/k/v projection -> per-head q/k norm + rotary + cache write (one kernel; in a
+prefill step of head size 64 or 128 the epilogue of the projection itself) ->
 attention over the cache -> output projection (reference: engine/engine.py:472-493; the residual
 add belongs to the block). The same forward serves whole prompts, continued chunks and single
 tokens: the step context says where each token row sits, the cache says what came before.
@@ -18,6 +19,9 @@ class GQAAttention(Part):
     # forward takes residual= and a deferred norm (see parts.block); measured slower than the separate
     # add+norm kernel on B200 (the small kernel hides behind the next product's weight prefetch), so off
     fuses_residual = False
+    # how full the last wave of the tensor-core product's tiles must be for a prefill step's projection
+    # to run as that product with norm, rotation and cache write in its epilogue (csrc.api.gemm_tc_qkv)
+    qkv_epilogue_min_fill = 0.8
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
@@ -79,9 +83,17 @@ class GQAAttention(Part):
         dtype, dev = self.rt.dtype, self.rt.device
         nh, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
         table = ctx.tables[kv.group]
+        fusable = self.position is None or getattr(self.position, "fused_tables", False)
+        if dtype == torch.bfloat16 and fusable and self._qkv_in_epilogue(a):
+            # prefill: the projection's epilogue norms and rotates q and k and writes the cache
+            cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1)) if self.position else (None, None)
+            q = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
+            api.gemm_tc_qkv(a, self.w_qkv, q, self.q_norm.weight if self.q_norm else None,
+                            self.k_norm.weight if self.k_norm else None, cos, sin, s.qk_norm.eps if s.qk_norm else 0.0,
+                            ctx.row_pos, ctx.row_seq, table, kv.k, kv.v, nh, nkv, hd, write_kv=writes)
+            return self._attend(ctx, kv, table, q, residual)
         qkv = linear(a, self.w_qkv, ctx=ctx, allow_partial=True)
         cos = sin = None
-        fusable = self.position is None or getattr(self.position, "fused_tables", False)
         if self.position is not None:
             if fusable:
                 cos, sin = self.position.tables(max(self.max_positions, ctx.max_position + 1))
@@ -105,6 +117,25 @@ class GQAAttention(Part):
         q = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         api.qk_norm_rope_write(qkv, q, qn, kn, cos, sin, ctx.row_pos, ctx.row_seq, table, kv.k, kv.v, nh, nkv, hd, eps,
                                write_kv=writes)
+        return self._attend(ctx, kv, table, q, residual)
+
+    def _qkv_in_epilogue(self, a):
+        """Whether this step's projection runs as the tensor-core product with norm, rotation and
+        cache write in its epilogue: a prefill step (more rows than the decode forms take) of a
+        size where that product is the one ``linear`` would pick anyway."""
+        s = self.spec
+        M, K = a.shape
+        return (not isinstance(a, api.Normed) and M > api.TC_SKINNY_MAX_ROWS and K % 8 == 0
+                and s.head_dim in api.TC_QKV_HEAD_DIMS
+                and api.gemm_tc_fills_gpu(M, self.w_qkv.shape[0], self.qkv_epilogue_min_fill))
+
+    def _attend(self, ctx, kv, table, q, residual):
+        """Attention of the rotated queries over the cache, then the output projection."""
+        s = self.spec
+        dtype, dev = self.rt.dtype, self.rt.device
+        nh, nkv, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        window = s.window or 0
+        o = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         if dtype == torch.float32:
             api.attention_generic(q, o, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, nh, nkv, hd, window, s.scale)
         elif ctx.is_decode:

@@ -152,6 +152,33 @@ def test_products_that_add_into_the_residual_and_apply_the_deferred_norm(tmp_pat
         assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_prefill_projection_with_norm_rotation_and_cache_write_in_its_epilogue(tmp_path, monkeypatch, name):
+    """Prefill steps of more than 128 rows whose q/k/v projection norms, rotates and writes the cache
+    in the epilogue of the tensor-core product (forced here: the tiny sizes would not fill the GPU):
+    the kernel really runs, and prefill and the decoding from the cache it wrote stay within rounding
+    of the plain implementation."""
+    from dryft_challenge_htn_2026_b200.csrc import api
+    from dryft_challenge_htn_2026_b200.parts.attention import GQAAttention
+    folder = make_folder(tmp_path, name, seed=15)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY[name]["vocab_size"], L, 90 + i) for i, L in enumerate([100, 70, 33, 150])]
+    monkeypatch.setattr(GQAAttention, "qkv_epilogue_min_fill", 0.0)
+    seen = {"calls": 0}
+    inner = api.gemm_tc_qkv
+
+    def counting(*a, **k):
+        seen["calls"] += 1
+        return inner(*a, **k)
+
+    monkeypatch.setattr(api, "gemm_tc_qkv", counting)
+    steps = list(dk.Engine(folder, dtype=torch.bfloat16).generate(prompts, 12))
+    assert seen["calls"] == TINY[name]["num_hidden_layers"]
+    scale = max(1.0, float(plain.forward(cfg, t, prompts[0]).abs().max()))
+    for i, p in enumerate(prompts):
+        assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale
+
+
 def test_prefill_in_several_steps_gives_the_same_tokens(tmp_path):
     """Prompts that do not fit one prefill step (here: a limit of 50 tokens) are prefilled in groups of
     whole sequences and a long one in chunks; in float32 that changes no token."""

@@ -454,6 +454,58 @@ def test_gemm_tc(M, N, K):
         api.gemm_tc(rnd(70, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,K,before,new,norm,rope", [
+    (4, 2, 64, 264, [0, 100], [200, 129], True, True), (3, 1, 128, 512, [300, 0, 5], [140, 70, 1], True, True),
+    (2, 2, 128, 72, [0], [130], False, True), (5, 1, 64, 136, [64, 0], [100, 100], True, False)])
+def test_gemm_tc_qkv_epilogue(nh, nkv, hd, K, before, new, norm, rope):
+    """The q/k/v projection with norm, rotation and cache write in its epilogue against the plain
+    formulas in float32 on the unrounded product: q, and the rows of the paged cache it wrote; a
+    padding row, a last tile that is not full (widths that are no multiple of 256), no norm, no
+    rotation, and a layer that only reads the cache."""
+    s = paged_setup(before, new, nkv, hd, torch.bfloat16, seed=95)
+    T = s["n_tok"]
+    x = rnd(T + 1, K, dtype=torch.bfloat16, seed=96)
+    w = rnd((nh + 2 * nkv) * hd, K, dtype=torch.bfloat16, seed=97, scale=K ** -0.5)
+    qn = 1 + 0.1 * rnd(hd, seed=98) if norm else None
+    kn = 1 + 0.1 * rnd(hd, seed=99) if norm else None
+    cos, sin = plain.rope_tables(1e4, hd, 600)
+    cos_h, sin_h = cos[:, :hd // 2].contiguous().to(DEV), sin[:, :hd // 2].contiguous().to(DEV)
+    row_pos = torch.cat([s["row_pos"], torch.tensor([-1], dtype=torch.int32, device=DEV)])     # one padding row
+    row_seq = torch.cat([s["row_seq"], torch.zeros(1, dtype=torch.int32, device=DEV)])
+    # plain formulas on the float32 product
+    y = (x.float() @ w.float().t()).view(T + 1, nh + 2 * nkv, hd)
+    def norm_rope(v, nw):
+        if nw is not None:
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * nw
+        if rope:
+            c, sn = cos_h[row_pos[:T].long()][:, None, :], sin_h[row_pos[:T].long()][:, None, :]
+            v1, v2 = v[..., :hd // 2], v[..., hd // 2:]
+            v = torch.cat([v1 * c - v2 * sn, v2 * c + v1 * sn], -1)
+        return v
+    q_want = norm_rope(y[:T, :nh], qn)
+    k_want, v_want = norm_rope(y[:T, nh:nh + nkv], kn), y[:T, nh + nkv:]
+    k0, v0 = s["k_store"].clone(), s["v_store"].clone()
+    q = torch.full((T + 1, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    api.gemm_tc_qkv(x, w, q, qn, kn, cos_h if rope else None, sin_h if rope else None, 1e-6, row_pos, row_seq, s["table"],
+                    s["k_store"], s["v_store"], nh, nkv, hd)
+    api.gemm_tc_check()
+    close(q[:T].view(T, nh, hd), q_want, torch.bfloat16, "q")
+    assert bool(torch.isnan(q[T:].float()).all())                    # nothing is stored for the padding row
+    pages = s["table"][row_seq[:T].long(), (row_pos[:T] // 64).long()].long()
+    slots = (row_pos[:T] % 64).long()
+    close(s["k_store"][pages, :, slots], k_want, torch.bfloat16, "k in the cache")
+    close(s["v_store"][pages, :, slots], v_want, torch.bfloat16, "v in the cache")
+    touched = torch.zeros_like(k0, dtype=torch.bool)
+    touched[pages, :, slots] = True
+    assert torch.equal(s["k_store"][~touched], k0[~touched]) and torch.equal(s["v_store"][~touched], v0[~touched])
+    # a layer that reads another layer's cache: q only
+    s["k_store"].copy_(k0), s["v_store"].copy_(v0)
+    api.gemm_tc_qkv(x, w, q, qn, kn, cos_h if rope else None, sin_h if rope else None, 1e-6, row_pos, row_seq, s["table"],
+                    s["k_store"], s["v_store"], nh, nkv, hd, write_kv=False)
+    close(q[:T].view(T, nh, hd), q_want, torch.bfloat16, "q, read-only")
+    assert torch.equal(s["k_store"], k0) and torch.equal(s["v_store"], v0)
+
+
 @pytest.mark.parametrize("nh,nkv,hd,window,before,new", [
     (2, 1, 128, 0, [0], [128]), (8, 2, 128, 0, [0, 100, 0, 64, 130], [70, 150, 1, 64, 5]), (4, 4, 64, 0, [0, 100], [200, 129]),
     (3, 1, 64, 90, [0, 100], [200, 129]), (6, 2, 128, 40, [300, 0], [140, 400]),
