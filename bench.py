@@ -230,6 +230,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
+    ap.add_argument("--prefill-tokens", type=int, default=PROMPT, help="with --prefill-only: a prompt of another length")
     ap.add_argument("--timeline", action="store_true",
                     help="print where one decode step's time goes inside the graph (kernels built with start notes) and exit")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
@@ -263,8 +264,8 @@ def main():
     if args.timeline:
         return timeline(torch, dk, api, model, args.batch)
     if args.prefill_only:
-        ms, flops = time_prefill(torch, dk, model, PROMPT)
-        print(json.dumps({"prefill": {"value": round(PROMPT / ms * 1e3, 1), "tokens": PROMPT, "ms": round(ms, 3),
+        ms, flops = time_prefill(torch, dk, model, args.prefill_tokens)
+        print(json.dumps({"prefill": {"value": round(args.prefill_tokens / ms * 1e3, 1), "tokens": args.prefill_tokens, "ms": round(ms, 3),
                                       "layers": cfg.num_hidden_layers,
                                       "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
         return 0

@@ -75,16 +75,21 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// the clock is read only when the barrier is not through yet (most waits of the mma thread find it through)
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity)
-            : "memory");
-        if (ok) return true;
+        if (mbar_test(bar, parity)) return true;
         if (clock64() - t0 > WAIT_CYCLES) return false;
     }
 }
@@ -270,14 +275,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     } else if (warp == 8) {
         if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
             // S(j) = Q . K(j)^T into buffer (step + j) & 1
+            // descriptors: the start address sits in the low bits in units of 16 bytes, so a tile further on is an addition
+            const uint64_t dq = desc_k_major(q_s), dk = desc_k_major(k_s), dv = desc_n_major(v_s);
             auto issue_s = [&](int j) {
                 const uint32_t b = (step + j) & 1;
+                const uint64_t dkb = dk + (uint64_t)((b * KV_BYTES) >> 4);
 #pragma unroll
                 for (int hh = 0; hh < HALVES; hh++)
 #pragma unroll
                     for (int k = 0; k < 4; k++)
-                        umma_ss(t_s + b * BN, desc_k_major(q_s + hh * Q_ATOM_BYTES + k * 32),
-                                desc_k_major(k_s + b * KV_BYTES + hh * KV_ATOM_BYTES + k * 32), IDESC_S, (hh | k) != 0);
+                        umma_ss(t_s + b * BN, dq + (uint64_t)((hh * Q_ATOM_BYTES + k * 32) >> 4),
+                                dkb + (uint64_t)((hh * KV_ATOM_BYTES + k * 32) >> 4), IDESC_S, (hh | k) != 0);
                 umma_commit(bar_s + b);
             };
             bool ok = mbar_wait(bar_q, items & 1) && mbar_wait(bar_k + (step & 1), (step >> 1) & 1);
@@ -305,7 +313,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 fence_after();
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++)
-                    umma_ts(t_o, t_s + b * BN + k * 8, desc_n_major(v_s + b * KV_BYTES + k * 16 * 128), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
+                    umma_ts(t_o, t_s + b * BN + k * 8, dv + (uint64_t)((b * KV_BYTES + k * 16 * 128) >> 4), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
                 umma_commit(bar_o + b);
                 TRACE(6);
             }
