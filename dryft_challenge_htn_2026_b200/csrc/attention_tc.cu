@@ -35,6 +35,9 @@
 #endif
 static_assert(HD == 64 || HD == 128, "tensor-core prefill attention is built for head sizes 64 and 128");
 
+// Development only (-DATTN_TRACE): clock stamps of the first steps of one block's roles, and for
+// every (tile, head) item its start and end on the global timer, its SM and its number of steps;
+// read back with dk_attn_trace*. This is how the empty block slots and the idle mma thread were found.
 #ifdef ATTN_TRACE
 __device__ long long g_trace[512];
 #define TRACE(slot) do { if (blockIdx.x == 0 && items == 0 && i < 6) g_trace[(slot) + 16 * i] = clock64(); } while (0)
