@@ -31,9 +31,15 @@ def set_pdl(on):
         lib.dk_set_pdl(int(_pdl))
 
 
+_cuda_seen = False
+
+
 def _lib(source, defines=None):
-    if not torch.cuda.is_available():
-        raise KernelError("no CUDA device: the kernels of this library run on an NVIDIA B200 (sm_100a) only")
+    global _cuda_seen
+    if not _cuda_seen:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: the kernels of this library run on an NVIDIA B200 (sm_100a) only")
+        _cuda_seen = True
     key = (source, tuple(sorted((defines or {}).items())))
     fresh = key not in build._libs
     lib = build.load_lib(source, defines)
@@ -60,8 +66,24 @@ def _check(lib, err, what, kernels=1):
         raise KernelError(f"{what}: CUDA error {err} ({msg})")
 
 
+# torch's current stream as a raw pointer. The call through torch.cuda.current_stream() builds a Stream
+# object (3.6 us, a quarter of what a launch costs on the host: short prefill steps are bound by that);
+# the raw getter takes 0.1 us. One device: its index is looked up once.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_device_index = None
+
+
+def _stream_ptr():
+    global _device_index
+    if _raw_stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return _raw_stream(_device_index)
+
+
 def _stream():
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return c_void_p(_stream_ptr())
 
 
 def _p(t):
@@ -636,7 +658,7 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
         raise KernelError(f"attention_prefill_tc: head size {head_dim} (64 or 128) / heads {n_heads}:{n_kv_heads} not supported")
     if _tc_err is None:
         _tc_err = torch.zeros(1, dtype=torch.int32, device=q.device)
-    stream = torch.cuda.current_stream().cuda_stream
+    stream = _stream_ptr()
     sched = _attn_sched.get(stream)          # the kernel's work counter: launches of one stream share it, in turn
     if sched is None:
         sched = _attn_sched[stream] = torch.zeros(2, dtype=torch.int32, device=q.device)
@@ -644,7 +666,7 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
     _check(lib, lib.dk_attn_prefill_tc(_p(q), _p(out), _p(k_store), _p(v_store), c_longlong(q.shape[0]),
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
-                                       c_float(scale), _p(_tc_err), _p(sched), _stream()), "attention_prefill_tc")
+                                       c_float(scale), _p(_tc_err), _p(sched), c_void_p(stream)), "attention_prefill_tc")
 
 
 def kernel_trace():
