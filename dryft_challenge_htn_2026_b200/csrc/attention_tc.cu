@@ -88,11 +88,22 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // the clock is read only when the barrier is not through yet (most waits of the mma thread find it through)
+// try_wait lets the hardware suspend the thread for a while instead of having it poll: a polling
+// thread takes issue slots from the softmax warps of the other block on its scheduler
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
-        if (mbar_test(bar, parity)) return true;
+        if (mbar_try(bar, parity)) return true;
         if (clock64() - t0 > WAIT_CYCLES) return false;
     }
 }
@@ -191,8 +202,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // one barrier per stage / buffer: step t (counted over all items of the block) uses number t & 1
     uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 7, *bar_o = bars + 9;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
-    volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 12);  // [0] the item all roles work on, [1] a wait ran out
-    float* xch = reinterpret_cast<float*>(bars + 13);       // [2][256] row maxima / sums exchanged between the two threads of a row
+    // [1] a wait ran out; [2], [3]: the block's items, the k-th in slot 2 + (k & 1), written by the loader thread
+    volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 12);
+    float* xch = reinterpret_cast<float*>(bars + 14);       // [2][256] row maxima / sums exchanged between the two threads of a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
@@ -201,6 +213,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int b = 0; b < 2; b++)
             mbar_init(bar_k + b, 1), mbar_init(bar_v + b, 1), mbar_init(bar_s + b, 1), mbar_init(bar_o + b, 1), mbar_init(bar_p + b, 256);
         item_slot[1] = 0;
+        item_slot[2] = atomicAdd(&sched[0], 1);             // the block's first item
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -215,24 +228,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const uint32_t tmem = *tmem_slot;
     const uint32_t t_s = tmem, t_o = tmem + 128;           // S buffers (and P over them) at columns 0..63 and 64..127, O at 128..128+HD
 
+    // What an item (tile, head) is, as every role needs it.
+    struct Item {
+        int h, kvh, rows_here, flat0, min_pos, max_pos, pos0, q0, blk_lo, n_blk;
+        const int* pt;
+    };
+    auto item_of = [&](int item) {
+        Item it;
+        const int seq = tiles[2 * (item / nh)];
+        it.q0 = tiles[2 * (item / nh) + 1];
+        it.h = item % nh, it.kvh = it.h / (nh / nkv);
+        it.pos0 = seq_pos0[seq];
+        it.rows_here = min(BM, cu_q[seq + 1] - cu_q[seq] - it.q0);
+        it.flat0 = cu_q[seq] + it.q0;                      // first flat row of this tile
+        it.pt = page_table + (size_t)seq * pt_stride;
+        it.min_pos = it.pos0 + it.q0, it.max_pos = it.min_pos + it.rows_here - 1;
+        it.blk_lo = window > 0 ? max(0, it.min_pos - window + 1) / BN : 0;
+        it.n_blk = it.max_pos / BN - it.blk_lo + 1;
+        return it;
+    };
+    // loader only; t0 = the item's first step
+    auto load_kv = [&](const CUtensorMap* map, uint32_t stages, uint64_t* bar, const Item& it, uint32_t t0, int j) {
+        const uint32_t b = (t0 + j) & 1;
+        mbar_expect_tx(bar + b, KV_BYTES);
+        int page = it.pt[min(it.blk_lo + j, pt_stride - 1)];
+        if (page < 0) page = 0;                             // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
+        const int row = (page * nkv + it.kvh) * DK_PAGE;
+        for (int hh = 0; hh < HALVES; hh++)
+            tma_load_2d(stages + b * KV_BYTES + hh * KV_ATOM_BYTES, map, hh * 64, row, bar + b);
+    };
+    auto load_q = [&](const Item& it) {
+        mbar_expect_tx(bar_q, Q_BYTES);
+        for (int hh = 0; hh < HALVES; hh++) tma_load_2d(q_s + hh * Q_ATOM_BYTES, &map_q, it.h * HD + hh * 64, it.flat0, bar_q);
+    };
+
     uint32_t step = 0, items = 0;                          // steps and items this block has finished
-    int next_item = threadIdx.x == 0 ? atomicAdd(&sched[0], 1) : 0;
     for (;;) {
-    if (threadIdx.x == 0) item_slot[0] = next_item;
-    __syncthreads();
-    const int item = item_slot[0];
+    // the item's number was left by the loader thread before the block barrier that ended the last item
+    const int item = item_slot[2 + (items & 1)];
     if (item >= n_items || item_slot[1]) break;
-    if (threadIdx.x == 0) next_item = atomicAdd(&sched[0], 1);   // the one after: the answer is not needed before this item is done
-    const int seq = tiles[2 * (item / nh)], q0 = tiles[2 * (item / nh) + 1];
-    const int h = item % nh, kvh = h / (nh / nkv);
-    const int q_len = cu_q[seq + 1] - cu_q[seq], pos0 = seq_pos0[seq];
-    const int rows_here = min(BM, q_len - q0);
-    const int flat0 = cu_q[seq] + q0;                      // first flat row of this tile
-    const int* pt = page_table + (size_t)seq * pt_stride;
-    const int max_pos = pos0 + q0 + rows_here - 1, min_pos = pos0 + q0;
-    const int blk_hi = max_pos / BN;
-    const int blk_lo = window > 0 ? max(0, min_pos - window + 1) / BN : 0;
-    const int n_blk = blk_hi - blk_lo + 1;
+    const Item cur = item_of(item);
+    const int h = cur.h, rows_here = cur.rows_here, flat0 = cur.flat0, min_pos = cur.min_pos, pos0 = cur.pos0, q0 = cur.q0;
+    const int blk_lo = cur.blk_lo, n_blk = cur.n_blk;
 #ifdef ATTN_TRACE
     if (threadIdx.x == 0 && item < 4096) {
         unsigned smid;
@@ -245,35 +282,30 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // barriers are then in their phase (t >> 1) & 1.
     if (warp == 9) {
         if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
-            auto load_kv = [&](const CUtensorMap* map, uint32_t stages, uint64_t* bar, int j) {
-                const uint32_t b = (step + j) & 1;
-                mbar_expect_tx(bar + b, KV_BYTES);
-                int page = pt[min(blk_lo + j, pt_stride - 1)];
-                if (page < 0) page = 0;                     // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
-                const int row = (page * nkv + kvh) * DK_PAGE;
-                for (int hh = 0; hh < HALVES; hh++)
-                    tma_load_2d(stages + b * KV_BYTES + hh * KV_ATOM_BYTES, map, hh * 64, row, bar + b);
-            };
-            mbar_expect_tx(bar_q, Q_BYTES);
-            for (int hh = 0; hh < HALVES; hh++) tma_load_2d(q_s + hh * Q_ATOM_BYTES, &map_q, h * HD + hh * 64, flat0, bar_q);
-            load_kv(&map_k, k_s, bar_k, 0);
-            load_kv(&map_v, v_s, bar_v, 0);
-            if (n_blk > 1) load_kv(&map_k, k_s, bar_k, 1), load_kv(&map_v, v_s, bar_v, 1);
+            load_q(cur);
+            load_kv(&map_k, k_s, bar_k, cur, step, 0);
+            load_kv(&map_v, v_s, bar_v, cur, step, 0);
+            if (n_blk > 1) load_kv(&map_k, k_s, bar_k, cur, step, 1), load_kv(&map_v, v_s, bar_v, cur, step, 1);
+            // the block's next item, for every role to read after this item's last barrier. (Requesting that item's
+            // Q and first pages here too, as this one lets go of the buffers, was measured 3 us an item slower.)
+            item_slot[2 + ((items + 1) & 1)] = atomicAdd(&sched[0], 1);
+            bool ok = true;
             // in the order in which the stages come free: S(j) is done with K(j), then P.V(j-1) with V(j-1)
-            for (int j = 0; j + 2 < n_blk; j++) {
+            for (int j = 0; j + 2 < n_blk && ok; j++) {
                 const uint32_t t = step + j;
-                if (!mbar_wait(bar_s + (t & 1), (t >> 1) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }
-                load_kv(&map_k, k_s, bar_k, j + 2);
+                if (!mbar_wait(bar_s + (t & 1), (t >> 1) & 1)) { ok = false; break; }
+                load_kv(&map_k, k_s, bar_k, cur, step, j + 2);
                 if (j >= 1) {
-                    if (!mbar_wait(bar_o + ((t - 1) & 1), ((t - 1) >> 1) & 1)) { atomicExch(err, 3), item_slot[1] = 1; break; }
-                    load_kv(&map_v, v_s, bar_v, j + 1);
+                    if (!mbar_wait(bar_o + ((t - 1) & 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
+                    load_kv(&map_v, v_s, bar_v, cur, step, j + 1);
                 }
             }
-            if (n_blk > 2) {                                // the last value page: after P.V(n - 3)
+            if (ok && n_blk > 2) {                          // the last value page: after P.V(n - 3)
                 const uint32_t t = step + n_blk - 3;
-                if (mbar_wait(bar_o + (t & 1), (t >> 1) & 1)) load_kv(&map_v, v_s, bar_v, n_blk - 1);
-                else atomicExch(err, 3), item_slot[1] = 1;
+                ok = mbar_wait(bar_o + (t & 1), (t >> 1) & 1);
+                if (ok) load_kv(&map_v, v_s, bar_v, cur, step, n_blk - 1);
             }
+            if (!ok) atomicExch(err, 3), item_slot[1] = 1;
         }
     } else if (warp == 8) {
         if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
@@ -494,7 +526,7 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
                                  const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
                                  int* sched, cudaStream_t st) {
     if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
-    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 13 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
