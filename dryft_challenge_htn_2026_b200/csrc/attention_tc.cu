@@ -4,25 +4,30 @@
 // Formulas as attention_bf16.cu (reference: engine/fused.py:301-343): scores scaled by
 // scale*log2(e), running maximum and sum in float32, P rounded to bfloat16 before P.V.
 //
-// A block owns 128 consecutive queries of one sequence and one query head and walks the keys in
-// blocks of 128 (two cache pages).
-//   warp 9, one thread: TMA loads (Q once; K and V of each block as [64 keys x 64 columns] boxes,
-//       128-byte swizzle, straight from the page the table names).
+// A block works on items: 128 consecutive queries of one sequence and one query head. It walks the
+// item's keys in steps of 64 (one cache page).
+//   warp 9, one thread: TMA loads (Q once an item; K and V of each step as [64 keys x 64 columns]
+//       boxes, 128-byte swizzle, straight from the page the table names; two stages each), and
+//       the draw of the block's next item from the counter.
 //   warp 8, one thread: all tcgen05.mma:
-//       S[128 x 128] = Q.K^T  (both operands from shared memory),
+//       S[128 x 64] = Q.K^T   (both operands from shared memory) into one of two S buffers,
 //       O[128 x HD] += P.V    (P from tensor memory, V from shared memory, N-major).
-//   warps 0-7: softmax, two threads per query row (64 key columns each): they read their part of
+//   warps 0-7: softmax, two threads per query row (32 key columns each): they read their part of
 //       the row of S from tensor memory (tcgen05.ld) into registers, agree on the running maximum
 //       through shared memory, rescale their half of the row of O in tensor memory when the
-//       maximum moved, write P as bfloat16 back into tensor memory over S (tcgen05.st), and at the
-//       end normalise and store their half of the row of O.
-// K of the next block is fetched as soon as S has been computed, V as soon as P.V has: the loads
-// overlap the softmax and the other product. Two blocks fit on an SM (96 KB shared, 256 columns of
-// tensor memory each), so one block's softmax overlaps the other's mma.
+//       maximum moved, write P as bfloat16 back into tensor memory over their S buffer
+//       (tcgen05.st), and at the end normalise and store their half of the row of O.
+// Tensor memory: S0 | S1 | O = 64 + 64 + 128 columns. While the softmax warps work on S of step j,
+// the mma thread issues S of step j + 1 into the other buffer (as soon as P.V of step j - 1 has
+// consumed the P in it) and then P.V of step j: the softmax warps find the next S waiting, and
+// the two products of a block run under its own softmax. K of step j + 2 is fetched as soon as S
+// of step j has been computed, V as soon as P.V has. Two blocks fit on an SM (96 KB shared, 256
+// columns of tensor memory each).
 // The grid is persistent: two blocks an SM, each takes the next (tile, head) from a counter in
 // global memory until none is left. (With a block per tile the SMs did not take a new block while
 // one of their two was still running: the light tiles started only when a whole SM had drained,
-// and 40 % of the block slots stood empty.) The tiles come sorted by the keys they see, so the
+// and 40 % of the block slots stood empty. Ten warps of 96 registers fit an SM twice only if the
+// second block's warps fall on the schedulers the first left emptier, which a newcomer's do not.) The tiles come sorted by the keys they see, so the
 // heavy ones start first and the light ones fill the end.
 // Every mbarrier wait is bounded; a wait that runs out stores a code in *err, and the block still
 // frees its tensor memory and returns.
