@@ -26,8 +26,8 @@
 // The grid is persistent: two blocks an SM, each takes the next (tile, head) from a counter in
 // global memory until none is left. (With a block per tile the SMs did not take a new block while
 // one of their two was still running: the light tiles started only when a whole SM had drained,
-// and 40 % of the block slots stood empty. Ten warps of 96 registers fit an SM twice only if the
-// second block's warps fall on the schedulers the first left emptier, which a newcomer's do not.) The tiles come sorted by the keys they see, so the
+// and 40 % of the block slots stood empty. A likely cause, not verified: ten warps of 96 registers
+// fit an SM twice only if the second block's warps fall on the schedulers the first left emptier.) The tiles come sorted by the keys they see, so the
 // heavy ones start first and the light ones fill the end.
 // Every mbarrier wait is bounded; a wait that runs out stores a code in *err, and the block still
 // frees its tensor memory and returns.
