@@ -47,3 +47,15 @@ def test_gemm_tc_fills_gpu_is_about_the_last_wave():
     assert api.gemm_tc_fills_gpu(2048, 19456 // 2)            # 16 x 38 tiles: 4.1 waves
     assert not api.gemm_tc_fills_gpu(2048, 2560)              # 160 tiles on 148 SMs: a second wave of 12
     assert api.gemm_tc_fills_gpu(128 * 148, 256)
+
+
+def test_the_tensor_core_product_is_picked_for_prefill_only_where_its_tiles_fill_the_gpu():
+    """128 x 256 tiles, one persistent block an SM: the benchmark model's q/k/v and gated products fill
+    their waves at 2,048 tokens, its o and down projections (160 tiles) and short prompts do not,
+    and with a lower bar (what the tests use to force the path) everything does."""
+    assert api.gemm_tc_fills_gpu(2048, 6144) and api.gemm_tc_fills_gpu(2048, 19456)
+    assert not api.gemm_tc_fills_gpu(2048, 2560) and not api.gemm_tc_fills_gpu(512, 6144)
+    assert api.gemm_tc_fills_gpu(130, 640, 0.0)
+    for M, N in itertools.product((129, 512, 2048, 8192, 32768), (640, 2560, 6144, 19456)):
+        tiles = -(-M // 128) * -(-N // 256)
+        assert api.gemm_tc_fills_gpu(M, N) == (tiles / api.SM_COUNT / -(-tiles // api.SM_COUNT) >= 0.8)
