@@ -104,15 +104,14 @@ class GQAAttention(Part):
         qn = self.q_norm.weight if self.q_norm else None
         kn = self.k_norm.weight if self.k_norm else None
         eps = s.qk_norm.eps if s.qk_norm else 0.0
-        window = s.window or 0
-        o = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         if dtype == torch.bfloat16 and ctx.is_decode and self.fuse_decode:
             # q/k norm + rotation and the cache write inside the attention kernel
+            o = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
             nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
             ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
                                         lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, dev))
-            api.attention_decode_fused(qkv, o, qn, kn, cos, sin, eps, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window,
-                                       s.scale, nsplit, ws_acc, ws_ml, write_kv=writes)
+            api.attention_decode_fused(qkv, o, qn, kn, cos, sin, eps, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd,
+                                       s.window or 0, s.scale, nsplit, ws_acc, ws_ml, write_kv=writes)
             return linear(o, self.w_o, ctx=ctx, allow_partial=True, residual=residual)
         q = torch.empty((ctx.n_tok, nh * hd), dtype=dtype, device=dev)
         api.qk_norm_rope_write(qkv, q, qn, kn, cos, sin, ctx.row_pos, ctx.row_seq, table, kv.k, kv.v, nh, nkv, hd, eps,
