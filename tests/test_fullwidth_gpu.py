@@ -1,0 +1,59 @@
+"""Two layers at the benchmark model's widths (Qwen3-4B: 32 query and 8 key/value heads of 128, hidden
+2,560, feed-forward 9,728, vocabulary 151,936) with random weights: a ragged prefill whose logits in
+bfloat16 are compared with the library's own float32 path (which the other tests tie to the plain
+implementation at small sizes). At these sizes the prefill runs what the tiny configurations only
+reach when forced: the q/k/v product with norm, rotation and cache write in its epilogue, the gated
+product, and the tcgen05 attention with six times more (tile, head) items than blocks."""
+import numpy as np
+import pytest
+import torch
+
+import dryft_challenge_htn_2026_b200 as dk
+from dryft_challenge_htn_2026_b200.csrc import api
+from dryft_challenge_htn_2026_b200.parts.attention import GQAAttention
+
+pytestmark = pytest.mark.gpu
+
+WIDTHS = dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=2560, intermediate_size=9728,
+              num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+              rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=40960)
+
+
+def prefill_logits(cfg, prompts, dtype):
+    model = dk.random_model(cfg, seed=0, dtype=dtype)
+    runner = dk.Runner(model, sum((len(p) + 127) // 64 * 64 for p in prompts), max_slots=len(prompts))
+    slots = [runner.begin() for _ in prompts]
+    out = runner.step([(s, p, [len(p) // 2, len(p) - 1]) for s, p in zip(slots, prompts)])
+    torch.cuda.synchronize()
+    api.gemm_tc_check()
+    return out.float().cpu()
+
+
+def test_ragged_prefill_at_full_width_agrees_with_float32(monkeypatch):
+    cfg = dk.config_from_dict(WIDTHS)
+    rs = np.random.RandomState(3)
+    prompts = [rs.randint(0, cfg.vocab_size, n).tolist() for n in (1500, 700, 2048, 129, 3000)]
+    calls = {"qkv": 0, "attention": 0}
+    for name, key in (("gemm_tc_qkv", "qkv"), ("attention_prefill_tc", "attention")):
+        inner = getattr(api, name)
+
+        def counting(*a, _inner=inner, _key=key, **k):
+            calls[_key] += 1
+            return _inner(*a, **k)
+
+        monkeypatch.setattr(api, name, counting)
+    want = prefill_logits(cfg, prompts, torch.float32)
+    assert calls == {"qkv": 0, "attention": 0}                       # the float32 path takes neither
+    got = prefill_logits(cfg, prompts, torch.bfloat16)
+    assert calls == {"qkv": 2, "attention": 2}                       # once a layer
+    monkeypatch.setattr(GQAAttention, "qkv_epilogue_min_fill", 2.0)  # the same with the separate norm/rotation kernel
+    apart = prefill_logits(cfg, prompts, torch.bfloat16)
+    scale = float(want.abs().max())
+    assert got.shape == (2 * len(prompts), cfg.vocab_size)
+    for name, x in (("epilogue", got), ("separate kernel", apart)):
+        err = float((x - want).abs().max())
+        assert err <= 0.03 * scale, f"{name}: {err} against float32 logits of size {scale}"
+    # where float32 has a clear winner, bfloat16 picks it too
+    top2 = want.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 0.06 * scale
+    assert bool((got.argmax(-1) == want.argmax(-1))[clear].all())
