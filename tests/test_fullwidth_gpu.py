@@ -57,3 +57,31 @@ def test_ragged_prefill_at_full_width_agrees_with_float32(monkeypatch):
     top2 = want.topk(2, -1).values
     clear = (top2[:, 0] - top2[:, 1]) > 0.06 * scale
     assert bool((got.argmax(-1) == want.argmax(-1))[clear].all())
+
+
+def stepped_logits(cfg, prompts, forced, dtype):
+    """Prefill, then len(forced) decode steps with given tokens; the logits of every decode step."""
+    model = dk.random_model(cfg, seed=0, dtype=dtype)
+    runner = dk.Runner(model, sum((len(p) + len(forced) + 127) // 64 * 64 for p in prompts), max_slots=len(prompts))
+    slots = [runner.begin() for _ in prompts]
+    runner.step([(s, p, []) for s, p in zip(slots, prompts)])
+    out = [runner.step([(s, [int(tok[i])], [0]) for i, s in enumerate(slots)]).float().cpu() for tok in forced]
+    torch.cuda.synchronize()
+    api.gemm_tc_check()
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("batch", [8, 20])
+def test_decode_steps_at_full_width_agree_with_float32(batch):
+    """Decode steps of 8 rows (the streaming product) and of 20 rows (the tensor-core product in its
+    decode form) over ragged caches, split-key attention and its merge, at the benchmark widths."""
+    cfg = dk.config_from_dict(WIDTHS)
+    rs = np.random.RandomState(5)
+    prompts = [rs.randint(0, cfg.vocab_size, int(n)).tolist() for n in rs.randint(60, 700, batch)]
+    forced = rs.randint(0, cfg.vocab_size, (4, batch))
+    want = stepped_logits(cfg, prompts, forced, torch.float32)
+    got = stepped_logits(cfg, prompts, forced, torch.bfloat16)
+    scale = float(want.abs().max())
+    assert got.shape == (4, batch, cfg.vocab_size)
+    err = float((got - want).abs().max())
+    assert err <= 0.03 * scale, f"{err} against float32 logits of size {scale}"
