@@ -71,10 +71,11 @@ def stepped_logits(cfg, prompts, forced, dtype):
     return torch.stack(out)
 
 
-@pytest.mark.parametrize("batch", [8, 20])
+@pytest.mark.parametrize("batch", [8, 20, 64])
 def test_decode_steps_at_full_width_agree_with_float32(batch):
     """Decode steps of 8 rows (the streaming product) and of 20 rows (the tensor-core product in its
-    decode form) over ragged caches, split-key attention and its merge, at the benchmark widths."""
+    decode form; at 64 rows also the two-deep rings of the split-key attention) over ragged caches,
+    split-key attention and its merge, at the benchmark widths."""
     cfg = dk.config_from_dict(WIDTHS)
     rs = np.random.RandomState(5)
     prompts = [rs.randint(0, cfg.vocab_size, int(n)).tolist() for n in rs.randint(60, 700, batch)]
