@@ -525,6 +525,11 @@ def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
                              hd ** -0.5)
     api.gemm_tc_check()
     close(out, ref_attention(q, s, nh, nkv, hd, window, hd ** -0.5), torch.bfloat16, "attention_prefill_tc")
+    again = torch.full_like(q, float("nan"))
+    api.attention_prefill_tc(q, again, s["k_store"], s["v_store"], tiles, s["cu_q"], s["pos0"], s["table"], nh, nkv, hd, window,
+                             hd ** -0.5)
+    assert torch.equal(again, out)                                   # which block took which item changes nothing
+    assert all(int(c.abs().sum()) == 0 for c in api._attn_sched.values())   # the work counter is left at zero
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 2560, 4096), (8, 2560, 9728), (5, 72, 304), (16, 1000, 2560), (11, 264, 5008)])
