@@ -643,6 +643,11 @@ def gemm_tc_check():
 # --------------------------------------------------------------- tensor-core prefill attention
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 TC_TILE_ROWS = 128
+# Keys a step of the kernel takes, 64 or 128 (a build option of attention_tc.cu). 64: two blocks an SM,
+# two softmax threads a query row. 128: one block an SM with all of its tensor memory, four threads a
+# row, half as many S instructions. Measured on B200, 32 heads of 128: 12.4 / 50.2 / 518 us at 512 /
+# 2,048 / 8,192 tokens with 64, 11.3 / 53.2 / 564 us with 128.
+TC_ATTENTION_STEP_KEYS = 64
 _attn_sched = {}
 
 
@@ -662,7 +667,7 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
     sched = _attn_sched.get(stream)          # the kernel's work counter: launches of one stream share it, in turn
     if sched is None:
         sched = _attn_sched[stream] = torch.zeros(2, dtype=torch.int32, device=q.device)
-    lib = _lib("attention_tc.cu", {"HD": head_dim})
+    lib = _lib("attention_tc.cu", {"HD": head_dim, "STEP_KEYS": TC_ATTENTION_STEP_KEYS})
     _check(lib, lib.dk_attn_prefill_tc(_p(q), _p(out), _p(k_store), _p(v_store), c_longlong(q.shape[0]),
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),

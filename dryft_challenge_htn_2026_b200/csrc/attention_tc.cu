@@ -1,6 +1,10 @@
 // Prefill attention on the 5th-generation tensor cores: ragged causal grouped-query flash
 // attention over the paged cache with S = Q.K^T and O += P.V as tcgen05.mma, accumulators in
-// tensor memory, tiles fed by TMA. Built per head size with -DHD=64 or -DHD=128.
+// tensor memory, tiles fed by TMA. Built per head size with -DHD=64 or -DHD=128, and with
+// -DSTEP_KEYS=64 (what is described below) or 128: steps of two pages, S buffers of 128 columns, four
+// softmax threads a row (warps 0-15), one block an SM holding all 512 columns of its tensor memory.
+// The latter halves the instructions of S but has no second block to fill its gaps; measured slower
+// from 2,048 tokens on (53 vs 50 us, 564 vs 518 us at 8,192), faster at 512 (11.3 vs 12.4 us).
 // Formulas as attention_bf16.cu (reference: engine/fused.py:301-343): scores scaled by
 // scale*log2(e), running maximum and sum in float32, P rounded to bfloat16 before P.V.
 //
@@ -63,12 +67,22 @@ __device__ __forceinline__ long long trace_now() {
 
 namespace {
 
-constexpr int BM = 128, BN = 64;                  // queries per block, keys per step (one cache page)
-static_assert(BN == DK_PAGE, "a step is one page of the cache");
+#ifndef STEP_KEYS
+#define STEP_KEYS 64
+#endif
+constexpr int BM = 128, BN = STEP_KEYS;           // queries per block, keys per step (one or two cache pages)
+static_assert(BN == DK_PAGE || BN == 2 * DK_PAGE, "a step is one or two pages of the cache");
+constexpr int PAGES = BN / DK_PAGE;
+constexpr int TPR = BN / 32;                      // softmax threads per query row: 32 key columns each
+constexpr int SOFT = 128 * TPR;                   // softmax threads; then the mma warp, then the loader warp
+constexpr int THREADS = SOFT + 64;
+constexpr int BLOCKS_PER_SM = BN == 64 ? 2 : 1;
+constexpr int TMEM_ALLOC = 2 * BN + 128 <= 256 ? 256 : 512;   // S0 | S1 | O; allocations are powers of two
+constexpr int OC = HD / TPR < 32 ? HD / TPR : 32; // columns of O a thread handles at a time
 constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms across the head
 constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;   // Q tile; one stage of K or of V
 constexpr int Q_ATOM_BYTES = BM * 128;            // the 128 query rows of one 64-column atom
-constexpr int KV_ATOM_BYTES = BN * 128;           // the 64 key rows of one 64-column atom
+constexpr int KV_ATOM_BYTES = BN * 128;           // the key rows of one 64-column atom
 constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -152,6 +166,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+// OC columns of a row of O (OC = 16 or 32)
+template <int N> __device__ __forceinline__ void tmem_ld_o(uint32_t taddr, uint32_t (&r)[N]) {
+    if constexpr (N == 32) tmem_ld32(taddr, r);
+    else tmem_ld16(taddr, r);
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -182,6 +208,10 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+template <int N> __device__ __forceinline__ void tmem_st_o(uint32_t taddr, const uint32_t (&r)[N]) {
+    if constexpr (N == 32) tmem_st32(taddr, r);
+    else tmem_st16(taddr, r);
+}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -195,7 +225,7 @@ __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::aft
 // Warp 8, one thread: every tcgen05.mma. Warp 9, one thread: every TMA load.
 // The per-step barriers (K, V, S, P, O) complete once a step and bar_q once an item: their phases
 // run on over the items (step, items count what this block has done so far).
-__global__ void __launch_bounds__(320, 2)
+__global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, bf16* out, const int* tiles, int n_items, const int* cu_q,
                        const int* seq_pos0, const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2,
@@ -209,21 +239,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     // [1] a wait ran out; [2], [3]: the block's items, the k-th in slot 2 + (k & 1), written by the loader thread
     volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 12);
-    float* xch = reinterpret_cast<float*>(bars + 14);       // [2][256] row maxima / sums exchanged between the two threads of a row
+    float* xch = reinterpret_cast<float*>(bars + 14);       // [2][SOFT] row maxima / sums exchanged between the threads of a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
     if (threadIdx.x == 0) {
         mbar_init(bar_q, 1);
         for (int b = 0; b < 2; b++)
-            mbar_init(bar_k + b, 1), mbar_init(bar_v + b, 1), mbar_init(bar_s + b, 1), mbar_init(bar_o + b, 1), mbar_init(bar_p + b, 256);
+            mbar_init(bar_k + b, 1), mbar_init(bar_v + b, 1), mbar_init(bar_s + b, 1), mbar_init(bar_o + b, 1), mbar_init(bar_p + b, SOFT);
         item_slot[1] = 0;
         item_slot[2] = atomicAdd(&sched[0], 1);             // the block's first item
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 8) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256)
+    constexpr int MMA_WARP = SOFT / 32, LOAD_WARP = MMA_WARP + 1;
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_ALLOC)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -231,7 +262,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_s = tmem, t_o = tmem + 128;           // S buffers (and P over them) at columns 0..63 and 64..127, O at 128..128+HD
+    const uint32_t t_s = tmem, t_o = tmem + 2 * BN;        // S buffers (and P over them) of BN columns each, then O of HD columns
 
     // What an item (tile, head) is, as every role needs it.
     struct Item {
@@ -256,11 +287,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto load_kv = [&](const CUtensorMap* map, uint32_t stages, uint64_t* bar, const Item& it, uint32_t t0, int j) {
         const uint32_t b = (t0 + j) & 1;
         mbar_expect_tx(bar + b, KV_BYTES);
-        int page = it.pt[min(it.blk_lo + j, pt_stride - 1)];
-        if (page < 0) page = 0;                             // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
-        const int row = (page * nkv + it.kvh) * DK_PAGE;
-        for (int hh = 0; hh < HALVES; hh++)
-            tma_load_2d(stages + b * KV_BYTES + hh * KV_ATOM_BYTES, map, hh * 64, row, bar + b);
+        for (int pg = 0; pg < PAGES; pg++) {
+            int page = it.pt[min((it.blk_lo + j) * PAGES + pg, pt_stride - 1)];
+            if (page < 0) page = 0;                         // a page the sequence does not hold (past its end, or given back by a window): any page will do, its keys are masked
+            const int row = (page * nkv + it.kvh) * DK_PAGE;
+            for (int hh = 0; hh < HALVES; hh++)
+                tma_load_2d(stages + b * KV_BYTES + hh * KV_ATOM_BYTES + pg * (DK_PAGE * 128), map, hh * 64, row, bar + b);
+        }
     };
     auto load_q = [&](const Item& it) {
         mbar_expect_tx(bar_q, Q_BYTES);
@@ -285,7 +318,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
     // Step j of the item is step t = step + j of the block; it uses stage / buffer / barrier t & 1, whose
     // barriers are then in their phase (t >> 1) & 1.
-    if (warp == 9) {
+    if (warp == LOAD_WARP) {
         if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
             load_q(cur);
             load_kv(&map_k, k_s, bar_k, cur, step, 0);
@@ -312,7 +345,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (!ok) atomicExch(err, 3), item_slot[1] = 1;
         }
-    } else if (warp == 8) {
+    } else if (warp == MMA_WARP) {
         if (lane == 0) {  // ------------------------------------------------------------ every tcgen05.mma
             // S(j) = Q . K(j)^T into buffer (step + j) & 1
             // descriptors: the start address sits in the low bits in units of 16 bytes, so a tile further on is an addition
@@ -359,13 +392,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (!ok) atomicExch(err, 1), item_slot[1] = 1;
         }
-    } else {  // ------------------------------------------------------------------ softmax, two threads a row
-        const int r = threadIdx.x & 127, half = threadIdx.x >> 7;   // row within the tile = tensor-memory lane; column half
+    } else {  // ------------------------------------------------------------------ softmax, TPR threads a row
+        const int r = threadIdx.x & 127, part = threadIdx.x >> 7;   // row within the tile = tensor-memory lane; which 32 key columns
         const bool valid = r < rows_here;
         const int qpos = pos0 + q0 + r;
         const int key_lo = window > 0 ? max(0, qpos - window + 1) : 0;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const int col0 = half * (BN / 2);                    // this thread's key columns within a step
+        const int col0 = part * 32;                          // this thread's key columns within a step
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
@@ -397,29 +430,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // sl2 > 0: scaling keeps the order
             // the row's maximum is over both threads of the row; once both have been here, both have read their S
             // (P of one goes over columns of S that the other reads)
-            xch[(i & 1) * 256 + threadIdx.x] = mx;
+            xch[(i & 1) * SOFT + threadIdx.x] = mx;
             if (threadIdx.x == 0) TRACE(7);
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + ((threadIdx.x >> 5) & 3)), "n"(32 * TPR) : "memory");   // the warps that share these rows
             if (threadIdx.x == 0) TRACE(3);
-            float m_new = fmaxf(m, fmaxf(mx, xch[(i & 1) * 256 + (threadIdx.x ^ 128)]));
+            float m_new = fmaxf(m, mx);
+#pragma unroll
+            for (int o = 1; o < TPR; o++) m_new = fmaxf(m_new, xch[(i & 1) * SOFT + ((threadIdx.x + 128 * o) & (SOFT - 1))]);
             // a maximum that moved by less than 8 (a factor 256) keeps the old reference: P stays well inside
             // float32 / bfloat16 range, the final O / l is the same, and O need not be rescaled
             if (m != -INFINITY && m_new - m < 8.f) m_new = m;
             const float ms = m_new == -INFINITY ? 0.f : m_new;
             const float alpha = m_new == m ? 1.f : ex2(m - ms);
             // O of the earlier steps is rescaled when the reference moved, once P.V of the last step is complete
-            // (that of the steps before it then is too). Each thread of a row takes half of the columns of O.
+            // (that of the steps before it then is too). Each thread of a row takes its share of the columns of O.
             if (i > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // tcgen05.ld/st are warp-wide: all lanes or none
                 if (!mbar_wait(bar_o + (b ^ 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
                 fence_after();
 #pragma unroll 1
-                for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-                    uint32_t o[32];
-                    tmem_ld32(t_o + lane_off + c, o);
+                for (int c = part * (HD / TPR); c < (part + 1) * (HD / TPR); c += OC) {
+                    uint32_t o[OC];
+                    tmem_ld_o(t_o + lane_off + c, o);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                    tmem_st32(t_o + lane_off + c, o);
+                    for (int j = 0; j < OC; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
+                    tmem_st_o(t_o + lane_off + c, o);
                 }
             }
             if (threadIdx.x == 0) TRACE(11);
@@ -445,20 +480,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (ok) ok = mbar_wait(bar_o + ((step + n_blk - 1) & 1), ((step + n_blk - 1) >> 1) & 1);
         // the row's sum is over both threads of the row
         xch[threadIdx.x] = l;
-        asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");   // the two warps that share these rows
-        l += xch[threadIdx.x ^ 128];
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + ((threadIdx.x >> 5) & 3)), "n"(32 * TPR) : "memory");   // the warps that share these rows
+#pragma unroll
+        for (int o = 1; o < TPR; o++) l += xch[(threadIdx.x + 128 * o) & (SOFT - 1)];
         if (ok) {
             fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(flat0 + r) * nh + h) * HD;
 #pragma unroll 1
-            for (int c = half * (HD / 2); c < (half + 1) * (HD / 2); c += 32) {
-                uint32_t o[32];
-                tmem_ld32(t_o + lane_off + c, o);
+            for (int c = part * (HD / TPR); c < (part + 1) * (HD / TPR); c += OC) {
+                uint32_t o[OC];
+                tmem_ld_o(t_o + lane_off + c, o);
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
+                    for (int j = 0; j < OC; j += 8) {
                         uint4 pk;
                         __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
@@ -483,9 +519,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     pdl_launch_dependents();
     if (threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) sched[0] = 0, sched[1] = 0;   // the last block leaves zeros for the next launch
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_ALLOC) : "memory");
     }
 }
 
@@ -531,7 +567,7 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
                                  const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
                                  int* sched, cudaStream_t st) {
     if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
-    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t) + 2 * 256 * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t) + 2 * SOFT * sizeof(float);
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -548,7 +584,8 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const long long n_items = (long long)n_tiles * nh;
     if (n_items > 0x7fffffffLL - 4 * sms) return (int)cudaErrorInvalidValue;
-    const int blocks = (int)(n_items < 2LL * sms ? n_items : 2LL * sms);
-    return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(320), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
+    const long long slots = (long long)BLOCKS_PER_SM * sms;
+    const int blocks = (int)(n_items < slots ? n_items : slots);
+    return dk_launch(attn_prefill_tc_kernel, dim3(blocks), dim3(THREADS), smem, st, mq, mk, mv, (bf16*)out, tiles, (int)n_items,
                      cu_q, seq_pos0, page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, err, sched);
 }

@@ -131,6 +131,6 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
             ("gemm_tc.cu", None), ("sampling.cu", None),
             ("sample_noalloc.cu", None)]
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
-    jobs += [("attention_tc.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
+    jobs += [("attention_tc.cu", {"HD": hd, "STEP_KEYS": 64}) for hd in head_dims if hd in (64, 128)]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
         return list(ex.map(lambda j: compile_lib(j[0], j[1], verbose), jobs))

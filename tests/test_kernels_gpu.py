@@ -510,11 +510,13 @@ def test_gemm_tc_qkv_epilogue(nh, nkv, hd, K, before, new, norm, rope):
     (2, 1, 128, 0, [0], [128]), (8, 2, 128, 0, [0, 100, 0, 64, 130], [70, 150, 1, 64, 5]), (4, 4, 64, 0, [0, 100], [200, 129]),
     (3, 1, 64, 90, [0, 100], [200, 129]), (6, 2, 128, 40, [300, 0], [140, 400]),
     (16, 4, 64, 0, [0, 100, 37, 64, 300], [700, 450, 300, 129, 1000]), (16, 2, 128, 200, [50, 0, 500], [900, 640, 1100])])
-def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
+@pytest.mark.parametrize("step_keys", [64, 128])
+def test_attention_prefill_tc(nh, nkv, hd, window, before, new, step_keys, monkeypatch):
     """The tcgen05 prefill attention against the float32 reference: ragged chunks on top of cached
     tokens, several key blocks per tile (rescaling of O), group sizes 1..8, a window, padding rows;
     the last two cases have more (tile, head) items than the grid has blocks, so that a block works
     through several, with odd and even numbers of steps, on the same barriers."""
+    monkeypatch.setattr(api, "TC_ATTENTION_STEP_KEYS", step_keys)    # both builds: steps of one page (the default) and of two
     s = paged_setup(before, new, nkv, hd, torch.bfloat16, seed=90)
     q = rnd(s["n_tok"], nh * hd, dtype=torch.bfloat16, seed=91)
     tiles = sorted(((before[i] + min(q0 + 128, new[i]), i, q0) for i in range(len(new)) for q0 in range(0, new[i], 128)),
