@@ -1,34 +1,54 @@
-"""Decode and prefill throughput of the Qwen3-4B layer sizes with random weights on one B200.
+"""Decode and prefill throughput of Qwen3 layer sizes with random weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--size 4b|8b|14b] [--batch 8] [--layers N]
+                    [--impl ours|reference]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at the default batch of 8: K decode
-steps of the captured decode loop, timed with CUDA events after W warm-up steps, every sequence
-with about 3,000 tokens of context already cached (a 2,048-token prompt, ragged 1,024..2,048 for
-batches above one, plus 1,024 tokens decoded so far: the midpoint of a 4,096-token context).
-``e2e`` is the same measured through ``Engine.generate`` (host token lists in, host tokens out).
-``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode step to the bytes it must
-read; ``points`` hold batch 1 and 64. The weights (8 GB) are far larger than L2, so no flush is
-needed between steps. For more than one GPU it says so and exits with 2: this library runs on one.
+steps of the generation loop's own decode state (CUDA-graph replay), timed with CUDA events after W
+warm-up steps, every sequence at the midpoint of the size's workload: for ``4b`` a 2,048-token
+prompt (ragged 1,024..2,048 above batch 1) plus 1,024 tokens decoded so far of a 4,096-token
+context; ``8b`` 1,024 + 512 of 1,024; ``14b`` 2,048 + 256 of 512. ``e2e`` is the same measured
+through ``Engine.generate`` (host token lists in, host tokens out). ``prefill`` is one 2,048-token
+prompt; ``roofline`` relates the decode step to the bytes it must read; ``points`` hold the size's
+other two batch sizes, each with its own step time, roofline fraction and clocks. The weights (8 to
+28 GB) are far larger than L2, so no flush is needed between steps. For more than one GPU it says
+so and exits with 2: this library runs on one.
+
+``--impl reference`` times the unmodified reference engine (a copy of its folder under
+``baseline/_ref``) through its own ``Engine(model_path)`` and ``Engine.generate`` on a model folder
+of the same sizes written here with plain torch; nothing of this library is imported on that arm.
 """
 import argparse
+import contextlib
 import json
 import os
+import shutil
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, hidden_size=2560, intermediate_size=9728,
-                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
-                rope_theta=1000000.0, tie_word_embeddings=True, max_position_embeddings=40960)
-CONTEXT = 4096
-PROMPT = 2048
-DECODED_SO_FAR = 1024
+_COMMON = dict(architectures=["Qwen3ForCausalLM"], vocab_size=151936, num_key_value_heads=8, head_dim=128,
+               rms_norm_eps=1e-6, rope_theta=1000000.0, max_position_embeddings=40960)
+# layer sizes, and the workload each is quoted on: prompt length (ragged from half of it above batch 1 where
+# `ragged`), decode steps of the whole run (timed at their midpoint), batch sizes
+SIZES = {
+    "4b": dict(config=dict(_COMMON, hidden_size=2560, intermediate_size=9728, num_hidden_layers=36,
+                           num_attention_heads=32, tie_word_embeddings=True),
+               name="Qwen3-4B", prompt=2048, ragged=True, decode=2048, batches=(1, 8, 64)),
+    "8b": dict(config=dict(_COMMON, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
+                           num_attention_heads=32, tie_word_embeddings=False),
+               name="Qwen3-8B", prompt=1024, ragged=False, decode=1024, batches=(1, 8, 64)),
+    "14b": dict(config=dict(_COMMON, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40,
+                            num_attention_heads=40, tie_word_embeddings=False),
+                name="Qwen3-14B", prompt=2048, ragged=False, decode=512, batches=(1, 8, 32)),
+}
+PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -80,30 +100,57 @@ class ClockSampler:
         return {"sm_mhz": int(statistics.median(sm)), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def ragged_lengths(batch, seed):
+def prompt_lengths(size, batch, seed):
+    """Context each sequence holds when the timed steps begin: its prompt plus half of the run's decode steps."""
     import numpy as np
-    if batch == 1:
-        return [PROMPT + DECODED_SO_FAR]
+    w = SIZES[size]
+    so_far = w["decode"] // 2
+    if batch == 1 or not w["ragged"]:
+        return [w["prompt"] + so_far] * batch
     r = np.random.RandomState(seed)
-    return [int(x) + DECODED_SO_FAR for x in r.randint(PROMPT // 2, PROMPT + 1, batch)]
+    return [int(x) + so_far for x in r.randint(w["prompt"] // 2, w["prompt"] + 1, batch)]
 
 
-def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
-    """K decode steps of the generation loop's own decode state (graph replay), timed on the device."""
+def random_prompts(vocab, lens, seed):
     import numpy as np
+    rs = np.random.RandomState(seed + 1)
+    return [rs.randint(0, vocab, n).tolist() for n in lens]
+
+
+def kv_bytes_per_token(cfg):
+    return cfg["num_hidden_layers"] * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def weight_bytes(cfg):
+    """Bytes of bfloat16 weights a decode step reads: every matrix once, the head once (the embedding is
+    read by row only, so it counts only where it is also the head)."""
+    H, hd = cfg["hidden_size"], cfg["head_dim"]
+    per_layer = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * hd * H + H * cfg["num_attention_heads"] * hd \
+        + 3 * cfg["intermediate_size"] * H
+    return 2 * (per_layer * cfg["num_hidden_layers"] + cfg["vocab_size"] * H)
+
+
+def prefill_flops(cfg, tokens):
+    H, hd, nh = cfg["hidden_size"], cfg["head_dim"], cfg["num_attention_heads"]
+    per_layer = (nh + 2 * cfg["num_key_value_heads"]) * hd * H + H * nh * hd + 3 * cfg["intermediate_size"] * H
+    L = cfg["num_hidden_layers"]
+    return 2 * per_layer * L * tokens + 4 * nh * hd * tokens * (tokens + 1) / 2 * L + 2 * cfg["vocab_size"] * H
+
+
+# ------------------------------------------------------------------------------------ this library
+def time_decode(torch, dk, model, cfg, size, batch, steps, warmup, seed):
+    """K decode steps of the generation loop's own decode state (graph replay), timed on the device."""
     from dryft_challenge_htn_2026_b200.csrc import api
     from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
     from dryft_challenge_htn_2026_b200.sampling import SamplingParams
 
-    lens = ragged_lengths(batch, seed)
+    lens = prompt_lengths(size, batch, seed)
     total_new = warmup + steps + 8
     need = sum((n + total_new + 63) // 64 * 64 for n in lens)
     runner = dk.Runner(model, need, max_slots=max(batch, 1))
     backend = GpuBackend(runner, use_graph=True)
-    rs = np.random.RandomState(seed + 1)
-    prompts = [rs.randint(0, model.spec.vocab_size, n).tolist() for n in lens]
-    params = SamplingParams(total_new)
-    backend.start(prompts, params, [0] * batch).wait()     # prefill (in steps of at most 32k tokens) and the first token
+    prompts = random_prompts(model.spec.vocab_size, lens, seed)
+    backend.start(prompts, SamplingParams(total_new), [0] * batch).wait()    # prefill (steps of at most 32k tokens), first token
     st = backend.state
     count0 = api.launch_count()
     st.body(advance=False, out_tok=torch.empty_like(st.ctx.tok))
@@ -113,7 +160,7 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
         st.run()
     torch.cuda.synchronize()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    with (sampler or ClockSampler()) as cs:
+    with ClockSampler() as cs:
         torch.cuda.synchronize()
         ev[0].record()
         for _ in range(steps):
@@ -122,9 +169,7 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
         torch.cuda.synchronize()
     ms = ev[0].elapsed_time(ev[1]) / steps
     ctx_mean = sum(lens) / batch + warmup + steps / 2
-    kv_bytes = sum(g.request.n_kv_heads * g.request.head_dim * 2 * len(g.entries) * 2
-                   for g in runner.cache.groups if hasattr(g, "pool"))
-    step_bytes = model.weight_bytes_per_step() + batch * ctx_mean * kv_bytes
+    step_bytes = model.weight_bytes_per_step() + batch * ctx_mean * kv_bytes_per_token(cfg)
     backend.finish()
     del st, backend, runner
     torch.cuda.empty_cache()
@@ -132,44 +177,7 @@ def time_decode(torch, dk, model, batch, steps, warmup, seed, sampler=None):
                 clocks=cs.summary())
 
 
-def timeline(torch, dk, api, model, batch):
-    """One decode step inside the captured graph: for every kernel the time from the end of its
-    wait for its predecessor to the end of the next kernel's wait (so overlap is counted once)."""
-    import collections
-
-    import numpy as np
-    from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
-    from dryft_challenge_htn_2026_b200.sampling import SamplingParams
-
-    lens = ragged_lengths(batch, 0)
-    runner = dk.Runner(model, sum((n + 64 + 63) // 64 * 64 for n in lens), max_slots=batch)
-    backend = GpuBackend(runner, use_graph=True)
-    rs = np.random.RandomState(1)
-    backend.start([rs.randint(0, model.spec.vocab_size, n).tolist() for n in lens], SamplingParams(48), [0] * batch).wait()
-    st = backend.state
-    st.capture()
-    for _ in range(32):
-        st.run()
-    torch.cuda.synchronize()
-    api.kernel_trace()
-    st.run()
-    st.run()
-    torch.cuda.synchronize()
-    ev = api.kernel_trace()
-    ev = ev[len(ev) // 2:] + [ev[-1]]                       # the second of the two steps
-    rows = collections.OrderedDict()
-    for a, b in zip(ev[:-1], ev[1:]):
-        rows.setdefault((a[1], int(a[2]), int(a[3])), []).append((b[0] - a[0]) / 1e3)
-    layers = len(model.spec.layers)
-    print(f"decode step at batch {batch}, {layers} layers: {(ev[-1][0] - ev[0][0]) / 1e3:.1f} us, {len(ev) - 1} launches")
-    for (src, grid, block), v in rows.items():
-        print(f"  {src:22s} {grid:6d} x {block:4d}  launches {len(v):4d}  mean {sum(v) / len(v):7.2f} us  total {sum(v):8.1f} us")
-    print("  first layer in order: " + "  ".join(f"{a[1].split('.')[0]}:{(b[0] - a[0]) / 1e3:.1f}" for a, b in list(zip(ev[:-1], ev[1:]))[:10]))
-    backend.finish()
-    return 0
-
-
-def time_prefill(torch, dk, model, tokens, iters=3):
+def time_prefill(torch, dk, model, cfg, tokens, iters=3):
     import numpy as np
     runner = dk.Runner(model, tokens + 64, max_slots=2)
     prompt = np.random.RandomState(7).randint(0, model.spec.vocab_size, tokens).tolist()
@@ -185,24 +193,16 @@ def time_prefill(torch, dk, model, tokens, iters=3):
         runner.end(slot)
         if i:
             times.append(e0.elapsed_time(e1))
-    s = model.spec
-    m = s.layers[0].mixer
-    per_layer = (m.num_heads + 2 * m.num_kv_heads) * m.head_dim * s.hidden_size + s.hidden_size * m.num_heads * m.head_dim \
-        + 3 * s.layers[0].feed_forward.intermediate_size * s.hidden_size
-    L = len(s.layers)
-    flops = 2 * per_layer * L * tokens + 4 * m.num_heads * m.head_dim * tokens * (tokens + 1) / 2 * L + 2 * s.vocab_size * s.hidden_size
     del runner
     torch.cuda.empty_cache()
-    return statistics.median(times), flops
+    return statistics.median(times), prefill_flops(cfg, tokens)
 
 
-def time_e2e(torch, dk, model, batch, steps, seed):
+def time_e2e(torch, dk, model, size, batch, steps, seed):
     """Decode tokens per second through Engine.generate: host lists in, host tokens out, from the
     first yielded step (end of prefill) to the last."""
-    import numpy as np
-    lens = ragged_lengths(batch, seed)
-    rs = np.random.RandomState(seed + 1)
-    prompts = [rs.randint(0, model.spec.vocab_size, n).tolist() for n in lens]
+    lens = prompt_lengths(size, batch, seed)
+    prompts = random_prompts(model.spec.vocab_size, lens, seed)
     eng = dk.Engine(model=model)
     list(eng.generate(prompts, 4))          # first call: allocations and the graph of this batch shape (kept by the engine)
     t_first = None
@@ -218,41 +218,33 @@ def time_e2e(torch, dk, model, batch, steps, seed):
     return batch * (n - 1) / (t_last - t_first), h2d, 4 * batch
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=48,
-                    help="untimed steps before the timed ones; the default outlasts the tens of milliseconds the SM clock "
-                         "takes to come back after the power-capped prefill")
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
-    ap.add_argument("--prefill-tokens", type=int, default=PROMPT, help="with --prefill-only: a prompt of another length")
-    ap.add_argument("--timeline", action="store_true",
-                    help="print where one decode step's time goes inside the graph (kernels built with start notes) and exit")
-    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
-    args = ap.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a folder of scripts without setup.py or pyproject.toml: pip cannot install "
-                          "it into baseline/_ref ('Neither setup.py nor pyproject.toml found')"}))
-        return 0
-    if args.gpus != 1:
-        print(f"bench.py: this library runs one model on one GPU; --gpus {args.gpus} is not supported")
-        return 2
-    warmup = max(3, args.warmup)
-    if args.timeline:
-        os.environ["DRYFT_KERNEL_TRACE"] = "1"     # read when the package's kernels are built and loaded
+def point(run, pk):
+    achieved = run["bytes"] / (run["ms"] * 1e-3) / 1e9
+    return {"value": round(run["tok_s"], 1), "ms_per_step": round(run["ms"], 4), "ctx_mean": round(run["ctx_mean"]),
+            "roofline_frac": round(achieved / pk["hbm_gbs"], 4), "clocks": run["clocks"]}
 
+
+def config_record(size, cfg, layers_full, batch, pk, **more):
+    w = SIZES[size]
+    rec = {"model": f"{w['name']} layer sizes", "global_batch": batch, "seq_len": w["prompt"] + w["decode"],
+           "parallelism": "1gpu", "layers": cfg["num_hidden_layers"], "layers_full": layers_full,
+           "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+           "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+           "tied_head": bool(cfg["tie_word_embeddings"]),
+           "prompt_len": f"{w['prompt']}" + (f" ({w['prompt'] // 2}..{w['prompt']} ragged above batch 1)" if w["ragged"] else ""),
+           "l2": "inputs larger than L2 (GBs of weights per step)", "peaks": pk["source"]}
+    rec.update(more)
+    return rec
+
+
+def run_ours(args):
     import torch
 
     import dryft_challenge_htn_2026_b200 as dk
     from dryft_challenge_htn_2026_b200.csrc import api
 
-    cfg_d = dict(QWEN3_4B)
+    size = args.size
+    cfg_d = dict(SIZES[size]["config"])
     full_layers = cfg_d["num_hidden_layers"]
     if args.layers:
         cfg_d["num_hidden_layers"] = args.layers
@@ -260,37 +252,33 @@ def main():
     api.set_pdl(bool(args.pdl))
     model = dk.random_model(cfg, seed=0, dtype=torch.bfloat16)
     pk = peaks()
+    warmup = max(3, args.warmup)
 
-    if args.timeline:
-        return timeline(torch, dk, api, model, args.batch)
     if args.prefill_only:
-        ms, flops = time_prefill(torch, dk, model, args.prefill_tokens)
-        print(json.dumps({"prefill": {"value": round(args.prefill_tokens / ms * 1e3, 1), "tokens": args.prefill_tokens, "ms": round(ms, 3),
-                                      "layers": cfg.num_hidden_layers,
+        ms, flops = time_prefill(torch, dk, model, cfg_d, args.prefill_tokens)
+        print(json.dumps({"prefill": {"value": round(args.prefill_tokens / ms * 1e3, 1), "tokens": args.prefill_tokens,
+                                      "ms": round(ms, 3), "layers": cfg.num_hidden_layers,
                                       "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
         return 0
-    main_run = time_decode(torch, dk, model, args.batch, args.steps, warmup, seed=0)
-    e2e_val, h2d, d2h = time_e2e(torch, dk, model, args.batch, args.steps, seed=0)
-    points, prefill = {}, None
+    main_run = time_decode(torch, dk, model, cfg_d, size, args.batch, args.steps, warmup, seed=0)
+    e2e_val, h2d, d2h = time_e2e(torch, dk, model, size, args.batch, args.steps, seed=0)
+    points, detail, prefill = {}, {}, None
     if not args.no_points:
-        for b in (1, 64):
-            points[f"decode_b{b}"] = round(time_decode(torch, dk, model, b, max(16, args.steps // 2), warmup, seed=b)["tok_s"], 1)
-        ms, flops = time_prefill(torch, dk, model, PROMPT)
-        prefill = {"value": round(PROMPT / ms * 1e3, 1), "tokens": PROMPT, "ms": round(ms, 3),
+        for b in SIZES[size]["batches"]:
+            if b != args.batch:
+                detail[f"decode_b{b}"] = point(time_decode(torch, dk, model, cfg_d, size, b, max(64, args.steps), warmup, seed=b), pk)
+                points[f"decode_b{b}"] = detail[f"decode_b{b}"]["value"]
+        ms, flops = time_prefill(torch, dk, model, cfg_d, PREFILL_TOKENS)
+        prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
                    "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     out = {
-        "metric": f"decode tok/s at batch {args.batch} (Qwen3-4B, bf16)", "value": round(main_run["tok_s"], 1), "unit": "tok/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms"], 4),
+        "metric": f"decode tok/s at batch {args.batch} ({SIZES[size]['name']}, bf16)", "value": round(main_run["tok_s"], 1),
+        "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids",
-        "config": {"model": "Qwen3-4B layer sizes", "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "1gpu",
-                   "layers": cfg.num_hidden_layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
-                   "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": True,
-                   "prompt_len": "2048 (1024..2048 ragged above batch 1)", "ctx_mean_timed": round(main_run["ctx_mean"]),
-                   "l2": "inputs larger than L2 (8 GB of weights per step)", "pdl": bool(args.pdl),
-                   "peaks": pk["source"]},
+        "config": config_record(size, cfg_d, full_layers, args.batch, pk, ctx_mean_timed=round(main_run["ctx_mean"]),
+                                pdl=bool(args.pdl)),
         "clocks": main_run["clocks"],
         "e2e": {"value": round(e2e_val, 1), "unit": "tok/s", "h2d_bytes_per_step": round(h2d), "d2h_bytes_per_step": d2h},
         "gpu_launches": main_run["launches"] * args.steps,
@@ -300,8 +288,216 @@ def main():
     if prefill is not None:
         out["prefill"] = prefill
         out["points"] = points
+        out["points_detail"] = detail
     print(json.dumps(out))
     return 0
+
+
+# ------------------------------------------------------------------------------ the reference arm
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+# The reference's own switches (engine/engine.py:31,98; engine/fused.py:19), set in the environment before it
+# is imported. Speculative decoding and fp8 prefill products are not part of the metric (plain bf16 decoding).
+# ENGINE_PDL=0: the reference patches the C launcher that Triton 3.1 generates; with the Triton of this image
+# the patched text is not found, every fused kernel then fails to compile (AssertionError) and its self-test
+# falls back to its torch ops, 5 times slower. Without the patch its fused Triton ops pass their self-test.
+REF_ENV = {"ENGINE_SPEC": "0", "ENGINE_FP8": "0", "ENGINE_PDL": "0"}
+
+
+def reference_source():
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            return json.load(f).get("reference_path") or ""
+    except Exception:
+        return ""
+
+
+def install_reference():
+    """baseline/_ref: an unmodified copy of the reference's folder (it has no setup.py or pyproject.toml
+    for pip to install). Returns None, or the reason it is not there."""
+    if os.path.isfile(os.path.join(REF_DIR, "engine", "engine.py")):
+        return None
+    src = os.environ.get("DRYFT_REFERENCE") or reference_source()
+    if not src or not os.path.isfile(os.path.join(src, "engine", "engine.py")):
+        return f"no copy of the reference under baseline/_ref and no source folder to copy it from ({src or 'none named'})"
+    os.makedirs(os.path.dirname(REF_DIR), exist_ok=True)
+    shutil.copytree(src, REF_DIR, ignore=shutil.ignore_patterns(".git", "__pycache__"))
+    return None
+
+
+def write_model_folder(torch, cfg, folder, seed=0, dev="cuda"):
+    """config.json (rope_theta at the top level, as the reference reads it) and one safetensors file per
+    layer with the checkpoint names of Qwen3ForCausalLM; matrices N(0, 0.02), norm weights 1 + N(0, 0.1)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(dict(cfg, model_type="qwen3", hidden_act="silu", attention_bias=False), f)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    H, hd, I, V = cfg["hidden_size"], cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    mat = lambda *s: (0.02 * torch.randn(s, generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16).cpu()
+    nrm = lambda n: (1.0 + 0.1 * torch.randn(n, generator=gen, device=dev, dtype=torch.float32)).to(torch.bfloat16).cpu()
+    top = {"model.embed_tokens.weight": mat(V, H), "model.norm.weight": nrm(H)}
+    if not cfg["tie_word_embeddings"]:
+        top["lm_head.weight"] = mat(V, H)
+    save_file(top, os.path.join(folder, "model-top.safetensors"))
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        save_file({p + "input_layernorm.weight": nrm(H), p + "post_attention_layernorm.weight": nrm(H),
+                   p + "self_attn.q_norm.weight": nrm(hd), p + "self_attn.k_norm.weight": nrm(hd),
+                   p + "self_attn.q_proj.weight": mat(nh * hd, H), p + "self_attn.k_proj.weight": mat(nkv * hd, H),
+                   p + "self_attn.v_proj.weight": mat(nkv * hd, H), p + "self_attn.o_proj.weight": mat(H, nh * hd),
+                   p + "mlp.gate_proj.weight": mat(I, H), p + "mlp.up_proj.weight": mat(I, H),
+                   p + "mlp.down_proj.weight": mat(H, I)}, os.path.join(folder, f"model-layer{i:03d}.safetensors"))
+
+
+def ref_decode(torch, eng, prompts, steps, warmup, sample_clocks=False):
+    """Decode steps of the reference's generator, as its tests/bench.py:104-111 times a run: wall clock at
+    each yield; the timed steps are those between yield number ``warmup`` and yield ``warmup + steps``."""
+    stamps = []
+    gen = eng.generate(prompts, warmup + steps + 1)
+    cs = ClockSampler() if sample_clocks else contextlib.nullcontext()
+    with cs:
+        for _ in gen:
+            stamps.append(time.perf_counter())
+    assert len(stamps) == warmup + steps + 1
+    ms = (stamps[warmup + steps] - stamps[warmup]) / steps * 1e3
+    return ms, (cs.summary() if sample_clocks else None)
+
+
+def run_reference(args):
+    why = install_reference()
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+    os.environ.update({k: os.environ.get(k, v) for k, v in REF_ENV.items()})
+    real_stdout = sys.stdout
+    sys.stdout = sys.stderr                       # the reference prints its self-test results; the JSON line stays alone
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device")
+        sys.path.insert(0, os.path.join(REF_DIR, "engine"))
+        from engine import Engine                 # the reference's engine/engine.py, unmodified
+
+        size = args.size
+        w = SIZES[size]
+        cfg = dict(w["config"])
+        full_layers = cfg["num_hidden_layers"]
+        if args.layers:
+            cfg["num_hidden_layers"] = args.layers
+        pk = peaks()
+        warmup = max(3, args.warmup)
+        folder = tempfile.mkdtemp(prefix="dryft_ref_model_")
+        try:
+            t0 = time.time()
+            write_model_folder(torch, cfg, folder)
+            print(f"[bench] model folder written in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+            t0 = time.time()
+            eng = Engine(folder)                  # loads, self-tests its fused ops against its torch ops, picks a back end
+            print(f"[bench] reference engine ready in {time.time() - t0:.0f} s", file=sys.stderr, flush=True)
+        finally:
+            shutil.rmtree(folder, ignore_errors=True)
+        backend = type(eng.ops).__name__
+        import fused
+        backend += f" (PDL {'on' if getattr(fused, 'PDL', False) else 'off'})"
+        V = cfg["vocab_size"]
+
+        def decode_point(batch, equal, steps, seed, clocks=False):
+            lens = prompt_lengths(size, batch, seed)
+            if equal:
+                lens = [max(lens)] * batch
+            ms, c = ref_decode(torch, eng, random_prompts(V, lens, seed), steps, warmup, clocks)
+            ctx_mean = sum(lens) / batch + warmup + steps / 2
+            nbytes = weight_bytes(cfg) + batch * ctx_mean * kv_bytes_per_token(cfg)
+            return dict(ms=ms, tok_s=batch / ms * 1e3, bytes=nbytes, ctx_mean=ctx_mean, clocks=c)
+
+        decode_point(args.batch, False, 4, seed=0)                      # compiles what this shape needs
+        main_run = decode_point(args.batch, False, args.steps, seed=0, clocks=True)
+        points, detail, prefill = {}, {}, None
+        if not args.no_points:
+            psteps = max(16, min(64, args.steps))
+            if w["ragged"] and args.batch > 1:
+                # the reference runs a ragged batch as one stream per prompt length (engine/engine.py:1093-1105);
+                # with equal lengths the same batch is one stream
+                detail[f"decode_b{args.batch}_equal_lengths"] = point(decode_point(args.batch, True, psteps, seed=0, clocks=True), pk)
+            for b in w["batches"]:
+                if b != args.batch:
+                    equal = b > 8                  # 64 streams of one sequence each would only measure batch 1 again
+                    key = f"decode_b{b}" + ("_equal_lengths" if equal and w["ragged"] else "")
+                    detail[key] = point(decode_point(b, equal, psteps, seed=b, clocks=True), pk)
+            points = {k: v["value"] for k, v in detail.items()}
+            prompt = random_prompts(V, [PREFILL_TOKENS], 6)
+            times = []
+            for i in range(4):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in eng.generate(prompt, 1):
+                    pass
+                torch.cuda.synchronize()
+                if i:
+                    times.append((time.perf_counter() - t0) * 1e3)
+            ms = statistics.median(times)
+            prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
+                       "frac": round(prefill_flops(cfg, PREFILL_TOKENS) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                       "how": "wall clock of generate(prompt, 1), the reference's TTFT"}
+        achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
+        lens = prompt_lengths(size, args.batch, 0)
+        out = {
+            "impl": "reference",
+            "metric": f"decode tok/s at batch {args.batch} ({w['name']}, bf16)", "value": round(main_run["tok_s"], 1),
+            "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(main_run["ms"], 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+            "config": config_record(size, cfg, full_layers, args.batch, pk, ctx_mean_timed=round(main_run["ctx_mean"]),
+                                    reference_backend=backend,
+                                    reference_env=" ".join(f"{k}={os.environ[k]}" for k in sorted(REF_ENV)),
+                                    streams=len(set(lens))),
+            "clocks": main_run["clocks"],
+            # the reference's only interface is the host-side generator: host token lists in, host tokens out;
+            # value and e2e are the same measurement (wall clock between yields)
+            "e2e": {"value": round(main_run["tok_s"], 1), "unit": "tok/s",
+                    "h2d_bytes_per_step": round(sum(lens) * 8 / (warmup + args.steps + 1)), "d2h_bytes_per_step": 8 * args.batch},
+            "gpu_launches": None,
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4)},
+        }
+        if prefill is not None:
+            out["prefill"] = prefill
+            out["points"] = points
+            out["points_detail"] = detail
+    except Exception as e:                         # the arm reports, it does not fail the round
+        import traceback
+        traceback.print_exc(file=sys.stderr)
+        out = {"impl": "reference", "unavailable": f"the reference engine did not run here: {type(e).__name__}: {str(e)[:300]}"}
+    finally:
+        sys.stdout = real_stdout
+    print(json.dumps(out))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=48,
+                    help="untimed steps before the timed ones; the default outlasts the tens of milliseconds the SM clock "
+                         "takes to come back after the power-capped prefill")
+    ap.add_argument("--size", default="4b", choices=sorted(SIZES), help="layer sizes and workload (default: Qwen3-4B)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the other batch sizes and the prefill")
+    ap.add_argument("--prefill-only", action="store_true", help="only the 2,048-token prefill (for profiling its kernels)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="with --prefill-only: a prompt of another length")
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on (1) or off (0)")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this library runs one model on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
 
 
 if __name__ == "__main__":
