@@ -37,6 +37,7 @@ class KVGroup:
         self.index, self.request, self.entries = index, request, list(entries)
         self.pool = PagePool(num_pages)
         self.pages = {}                                   # slot -> list of page ids (-1: given back)
+        self.first = {}                                   # slot -> index of the first page not yet given back
         self.store = None
         if allocate:
             self.store = torch.zeros((len(self.entries), 2, num_pages, request.n_kv_heads, PAGE, request.head_dim),
@@ -48,6 +49,7 @@ class KVGroup:
 
     def start(self, slot):
         self.pages[slot] = []
+        self.first[slot] = 0
 
     def ensure(self, slot, length):
         """Pages for positions [0, length) of the slot (those still inside the window)."""
@@ -64,13 +66,16 @@ class KVGroup:
             return
         first_needed = length - w + 1
         have = self.pages[slot]
-        for i, p in enumerate(have):
-            if p >= 0 and i * PAGE + PAGE - 1 < first_needed:
-                self.pool.free([p])
-                have[i] = -1
+        i = self.first[slot]
+        while i < len(have) and i * PAGE + PAGE - 1 < first_needed:
+            self.pool.free([have[i]])
+            have[i] = -1
+            i += 1
+        self.first[slot] = i
 
     def end(self, slot):
         self.pool.free([p for p in self.pages.pop(slot) if p >= 0])
+        del self.first[slot]
 
     def bytes(self):
         return 0 if self.store is None else self.store.numel() * self.store.element_size()
@@ -171,6 +176,11 @@ class Cache:
         rows = [g.pages[s] for s in slots]
         width = max([min_width] + [len(r) for r in rows])
         return [r + [-1] * (width - len(r)) for r in rows]
+
+    def pages_held(self, slot):
+        """Per key/value group the length of the slot's page list (pages given back included): it
+        changes exactly when a step's page tables have to be written anew."""
+        return tuple(len(g.pages[slot]) for g in self.groups if isinstance(g, KVGroup))
 
     def bytes(self):
         return sum(g.bytes() for g in self.groups)

@@ -6,7 +6,6 @@ the sizes a kernel supports); a kernel that cannot take a size raises ``KernelEr
 compute something else. There is no CPU or library fallback behind these functions.
 """
 import ctypes
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -48,6 +47,19 @@ def _lib(source, defines=None):
         lib.dk_set_pdl(int(_pdl))
         lib.dk_error_string.restype = ctypes.c_char_p
     return lib
+
+
+_sm_count = None
+
+
+def sm_count():
+    """Multiprocessors of the device the kernels run on; every launch plan is sized by it. Without
+    a CUDA device (plans looked at on another machine) the B200's 148."""
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count \
+            if torch.cuda.is_available() else 148
+    return _sm_count
 
 
 _launches = 0
@@ -173,12 +185,19 @@ def gather_rows_f32(src, rows, out):
 
 
 def qk_norm_rope_write(qkv, q_out, q_norm_w, k_norm_w, cos, sin, row_pos, row_seq, page_table, k_store, v_store,
-                       n_heads, n_kv_heads, head_dim, eps, write_kv=True):
+                       n_heads, n_kv_heads, head_dim, eps, write_kv=True, dense_out=None):
     """Per-head RMSNorm (weights may be None), rotate-half rotation (cos/sin [positions, hd/2]
     float32, may be None), q to q_out [T, nh*hd], k and v into the paged stores
-    [pages, n_kv, PAGE, hd] at each token's position. Rows with position < 0 are skipped."""
+    [pages, n_kv, PAGE, hd] at each token's position. Rows with position < 0 are skipped.
+    With ``dense_out`` [T, (nh + 2 nkv) * hd] the heads go there instead (q and k normalised and
+    rotated as asked, v copied) and neither q_out nor the cache is written."""
     width, n_tok = qkv.shape[1], qkv.shape[0]
     qkv, parts, n_parts, stride = _parts(qkv)
+    if dense_out is not None:
+        _need(dense_out, "dense_out", None, 2)
+        if tuple(dense_out.shape) != (n_tok, width):
+            raise KernelError(f"dense_out {tuple(dense_out.shape)} must have the projection's shape {(n_tok, width)}")
+        q_out = dense_out if q_out is None else q_out
     _need(qkv, "qkv", q_out.dtype, 2), _need(q_out, "q_out", None, 2)
     _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
     _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
@@ -189,7 +208,7 @@ def qk_norm_rope_write(qkv, q_out, q_norm_w, k_norm_w, cos, sin, row_pos, row_se
     if width != (n_heads + 2 * n_kv_heads) * head_dim:
         raise KernelError(f"qkv width {width} != (nh + 2 nkv) * hd")
     lib = _lib("elementwise.cu")
-    _check(lib, lib.dk_qk_norm_rope_write(_dt(q_out), _p(qkv), parts, n_parts, stride, _p(q_out), _p(q_norm_w),
+    _check(lib, lib.dk_qk_norm_rope_write(_dt(q_out), _p(qkv), parts, n_parts, stride, _p(q_out), _p(dense_out), _p(q_norm_w),
                                           _p(k_norm_w), _p(cos), _p(sin), _p(row_pos), _p(row_seq), _p(page_table),
                                           page_table.shape[1], _p(k_store), _p(v_store), n_tok, n_heads, n_kv_heads,
                                           head_dim, c_float(eps), int(bool(write_kv)), _stream()), "qk_norm_rope_write")
@@ -217,6 +236,9 @@ def _attn_lib(head_dim):
     return _lib("attention_bf16.cu", {"HD": head_dim})
 
 
+MMA_TILE_ROWS = 64   # queries a block of attention_prefill_bf16 takes
+
+
 def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_table, n_heads, n_kv_heads, head_dim,
                            window, scale):
     """Ragged causal attention of query chunks (tensor cores). tiles [n, 2] int32 = (sequence,
@@ -233,12 +255,14 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=8, resident_blocks=2 * 148):
+def decode_splits(n_seq, n_kv_heads, group, max_splits=8, resident_blocks=None):
     """Number of key splits for decode attention, fixed for a batch size (it must not depend on
     sequence lengths, which change under a captured graph). While all blocks fit the GPU at once
     (two per SM with the three-deep rings): as many splits as keep it so. Beyond that: enough for
     about six waves of blocks, which evens out sequences of unequal lengths (measured at batch 64:
     133 us unsplit, 115 us in four splits)."""
+    if resident_blocks is None:
+        resident_blocks = 2 * sm_count()
     blocks = n_seq * n_kv_heads * ((group + 15) // 16)
     if blocks <= resident_blocks:
         return max(1, min(max_splits, resident_blocks // blocks))
@@ -275,7 +299,6 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
 
 # ---------------------------------------------------------------------------------------- products
 MODE_STORE, MODE_STORE_F32, MODE_SILU = 0, 1, 2
-GEMV_MAX_ROWS = 64
 
 
 def sgemm(x, w, out, mode=MODE_STORE):
@@ -287,56 +310,6 @@ def sgemm(x, w, out, mode=MODE_STORE):
         raise KernelError(f"sgemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
     lib = _lib("gemm.cu")
     _check(lib, lib.dk_sgemm(_p(x), _p(w), _p(out), M, N, K, mode, _stream()), "sgemm")
-
-
-SM_COUNT = 148
-GEMV_BLOCKS_PER_SM = {1: 2, 2: 2, 4: 1, 8: 1}   # by 8-row batch tiles: what the kernel's registers allow at 8 warps
-
-
-def _batch_tiles(M):
-    return 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
-
-
-def gemv_plan(M, N, K, mode, allow_partial=False):
-    """(SK, warps, max_blocks). Every warp streams one unit (16 weight rows x one slice of K) on
-    its own; SK slices per tile are chosen so that all units fit on the GPU at once (one wave of
-    equal units is balanced by the memory system itself) with at least 4 chunks of 64 per slice."""
-    warps = 8
-    max_blocks = SM_COUNT * GEMV_BLOCKS_PER_SM[_batch_tiles(M)]
-    tiles, chunks = (N + 15) // 16, (K + 63) // 64
-    sk = 1
-    if allow_partial and mode != MODE_SILU:
-        while sk < 16 and tiles * sk * 2 <= max_blocks * warps and chunks >= 4 * sk * 2:
-            sk *= 2
-    return sk, warps, max_blocks
-
-
-def gemv_bf16(x, w, out=None, mode=MODE_STORE, plan=None):
-    """Skinny bfloat16 product for at most 64 rows of x. Returns ``out`` [M, N] (bfloat16 for
-    modes 0 and 2, float32 for mode 1), or, when the plan splits K (plan[0] > 1), a ``Partial``."""
-    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
-    M, K = x.shape
-    N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
-    if M > GEMV_MAX_ROWS or K % 8:
-        raise KernelError(f"gemv_bf16: {M} rows (max {GEMV_MAX_ROWS}) / inner size {K} (multiple of 8) not supported")
-    if w.shape[1] != K:
-        raise KernelError(f"gemv_bf16: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
-    sk, warps, max_blocks = plan or gemv_plan(M, N, K, mode)
-    ws = None
-    if sk > 1:
-        if mode == MODE_SILU:
-            raise KernelError("gemv_bf16: the SiLU epilogue cannot be split over K")
-        ws = torch.empty((sk, M, N), dtype=torch.float32, device=x.device)
-    else:
-        want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
-        if out is None:
-            out = torch.empty((M, N), dtype=want, device=x.device)
-        elif out.dtype != want or tuple(out.shape) != (M, N):
-            raise KernelError(f"gemv_bf16: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
-    lib = _lib("gemm.cu")
-    _check(lib, lib.dk_gemv_bf16(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, warps, max_blocks, _stream()),
-           "gemv_bf16")
-    return Partial(ws) if sk > 1 else out
 
 
 # ---------------------------------------------------------------------------------------- sampling
@@ -361,164 +334,88 @@ def sample(logits, temperature, seeds, pos, rows, ws_val, ws_idx, out_tok, advan
                               _p(out_tok), int(bool(advance)), _stream()), "sample", 2)
 
 
-# ------------------------------------------------------------------------------------- L2 prefetch
-def l2_prefetch(t, stream=None):
-    """Hints the whole tensor into L2 from ``stream`` (default: the current stream)."""
-    lib = _lib("elementwise.cu")
-    st = _stream() if stream is None else c_void_p(stream.cuda_stream)
-    _check(lib, lib.dk_l2_prefetch(_p(t), c_longlong(t.numel() * t.element_size()), st), "l2_prefetch")
-
-
 # ------------------------------------------------------------------- streaming product (M <= 16)
 STREAM_MAX_ROWS = 16
 # rows up to which the streaming product is the fastest: with 9 to 16 rows its copy of x doubles and
-# only one block fits an SM, and the tensor-core product in its decode form wins (measured at 12, 16, 17)
+# the tensor-core product in its decode form wins (measured at 12, 16, 17)
 STREAM_BEST_ROWS = 8
-STREAM_BUILD = None   # compile-time overrides of the kernel's stage size, ring depth and warp count (tuning)
+_STREAM_SMEM_BLOCK = 227 * 1024              # dynamic shared memory one block may ask for
+_STREAM_SMEM_PAIR = (228 * 1024) // 2 - 1024  # ... and what each of two blocks sharing an SM may use
+
+
+def _stream_smem(rows, K, sk, warps):
+    """Shared memory of a block of the streaming product: ``warps`` two-deep rings of 16 weight rows
+    x 256 columns, two buffers of the warps' sums, and the rows (8 or 16) of one slice of x. Must
+    equal smem_bytes() in gemv_stream.cu."""
+    mr = 8 if rows <= 8 else 16
+    per = ((K + sk - 1) // sk + 15) // 16 * 16
+    return warps * 2 * 16 * (256 * 2 + 16) + 2 * warps * 16 * mr * 4 + mr * (per * 2 + 16)
+
 
 def stream_plan(M, N, K, mode, allow_partial=False):
-    """(SK, blocks) for gemv_stream, or None if it cannot take the shape. Two persistent blocks
-    per SM; K is cut into the fewest slices that keep a block's piece of x in shared memory (2560
-    elements), and further (if the caller takes partial sums) while there are fewer than two
-    tiles per block (more slices cost the consumer more partial sums to add)."""
-    blocks = 2 * SM_COUNT
+    """(slices of K, blocks, streaming warps a block) for gemv_stream, or None if it cannot take
+    the shape. Four warps and two persistent blocks per SM while the rows of x leave room for two
+    blocks; for a longer K eight warps and one block per SM (as many bytes in flight); beyond that
+    K is cut into slices, which needs a caller that takes partial sums (never the SiLU epilogue).
+    With partial sums allowed K is cut further while there are fewer than two tiles per block (more
+    slices cost the consumer more partial sums to add)."""
+    sms = sm_count()
+
+    def shape(sk):
+        if _stream_smem(M, K, sk, 4) <= _STREAM_SMEM_PAIR:
+            return 4, 2 * sms
+        if _stream_smem(M, K, sk, 8) <= _STREAM_SMEM_BLOCK:
+            return 8, sms
+        if _stream_smem(M, K, sk, 4) <= _STREAM_SMEM_BLOCK:
+            return 4, sms
+        return None
+
     sk = 1
-    while ((K + sk - 1) // sk + 15) // 16 * 16 > 2560:
+    while shape(sk) is None:
         sk *= 2
+        if sk > 64:
+            return None
     if sk > 1 and (mode == MODE_SILU or not allow_partial):
         return None
+    warps, blocks = shape(sk)
     if allow_partial and mode != MODE_SILU:
         tiles = (N + 15) // 16
         while sk < 8 and tiles * sk < 2 * blocks and K // (sk * 2) >= 512:
             sk *= 2
-    return sk, blocks
+        warps, blocks = shape(sk)
+    return sk, blocks, warps
 
 
-class Added:
-    """The result of a product that has already been added into the float32 residual stream
-    ``h`` in place. ``sq`` [pieces, 16] float32 holds the sums of squares of the new h's rows
-    (row j in column j) in pieces, one per tile of the kernel: summed over the pieces they are
-    what an RMSNorm of h needs."""
-
-    def __init__(self, h, sq):
-        self.h, self.sq = h, sq
-
-
-class Normed:
-    """rmsnorm(h) * weight that has not been computed yet: a product that can (``gemv_stream``)
-    makes it from ``h`` and the sums of squares while it loads its input; anything else calls
-    ``tensor()``. It stands for h as it is now: use it before the next product is added into h."""
-
-    def __init__(self, h, sq, weight, eps, dtype):
-        self.h, self.sq, self.weight, self.eps, self.dtype = h, sq, weight, eps, dtype
-
-    @property
-    def shape(self):
-        return self.h.shape
-
-    def tensor(self):
-        out = torch.empty(self.h.shape, dtype=self.dtype, device=self.h.device)
-        add_rmsnorm(self.h, None, self.weight, self.eps, out)
-        return out
-
-
-_counters = {}
-
-
-def tile_counters(device, n):
-    """Zeroed int32 counters that kernels with an in-kernel meeting point (split-K slices of a
-    tile, key splits of a head) draw tickets from; every such kernel leaves them zero."""
-    if n > (1 << 16):
-        raise KernelError(f"{n} meeting points in one launch are more than the counters hold")
-    key = (device.type, device.index)
-    if key not in _counters:
-        _counters[key] = torch.zeros(1 << 16, dtype=torch.int32, device=device)
-    return _counters[key]
-
-
-def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None, residual=None, prefetch=None):
+def gemv_stream(x, w, out=None, mode=MODE_STORE, plan=None):
     """The weight-streaming skinny product (asynchronous copies into shared-memory rings,
-    tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Same results and
-    return convention as ``gemv_bf16``. ``x`` may be a ``Normed`` (the norm is applied while x is
-    loaded; modes STORE and SILU). With ``residual`` (float32 [M, N], mode STORE) the product is
-    added into it in place and an ``Added`` is returned. ``prefetch``: a contiguous tensor (the next
-    product's weights) that the kernel asks into L2 while it runs."""
-    lazy = isinstance(x, Normed)
-    if lazy:
-        if x.dtype != torch.bfloat16 or mode == MODE_STORE_F32 or residual is not None:
-            raise KernelError("gemv_stream: a deferred norm goes with bfloat16, modes STORE and SILU, and no residual")
-        _need(x.h, "h", torch.float32, 2), _need(x.sq, "sq", torch.float32, 2), _need(x.weight, "norm_w", torch.float32, 1)
-    else:
-        _need(x, "x", torch.bfloat16, 2)
-    _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2), _need(residual, "residual", torch.float32, 2)
+    tensor-core multiply) for at most 16 rows of x and K a multiple of 16. Returns ``out`` [M, N]
+    (bfloat16 for MODE_STORE and MODE_SILU, float32 for MODE_STORE_F32), or, when the plan splits K
+    (plan[0] > 1), a ``Partial``."""
+    _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
     M, K = x.shape
     N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
     if M > STREAM_MAX_ROWS or K % 16:
         raise KernelError(f"gemv_stream: {M} rows (max {STREAM_MAX_ROWS}) / inner size {K} (multiple of 16) not supported")
     if w.shape[1] != K:
         raise KernelError(f"gemv_stream: shapes x{tuple(x.shape)} w{tuple(w.shape)} do not match")
-    if lazy and (x.sq.shape[1] != 16 or x.weight.numel() != K):
-        raise KernelError("gemv_stream: the deferred norm's sums of squares or weight do not fit the input width")
-    if residual is not None and (mode != MODE_STORE or tuple(residual.shape) != (M, N)):
-        raise KernelError("gemv_stream: a residual goes with mode STORE and has the output's shape")
-    sk, blocks = plan or stream_plan(M, N, K, mode, residual is not None) or (0, 0)
-    if sk < 1 or blocks < sk or ((K + sk - 1) // sk + 15) // 16 * 16 > 2560:
-        raise KernelError(f"gemv_stream: K = {K} in {sk} slices on {blocks} blocks is not supported "
-                          "(a slice holds at most 2560 elements, and there is a block per slice at least)")
-    ws = sq = counters = None
+    sk, blocks, warps = plan or stream_plan(M, N, K, mode) or (0, 0, 0)
+    if sk < 1 or blocks < sk or warps not in (4, 8) or _stream_smem(M, K, sk, warps) > _STREAM_SMEM_BLOCK:
+        raise KernelError(f"gemv_stream: K = {K} in {sk} slices on {blocks} blocks of {warps} warps is not supported "
+                          f"(the {M} rows of a slice of x must fit a block's shared memory, and there is a block per slice at least)")
+    ws = None
     if sk > 1:
         if mode == MODE_SILU:
             raise KernelError("gemv_stream: the SiLU epilogue cannot be split over K")
         ws = torch.empty((sk, M, N), dtype=torch.float32, device=w.device)
-    if residual is not None:
-        sq = torch.empty(((N + 15) // 16, 16), dtype=torch.float32, device=w.device)
-        counters = tile_counters(w.device, (N + 15) // 16)
-    elif sk == 1:
+    else:
         want = torch.float32 if mode == MODE_STORE_F32 else torch.bfloat16
         if out is None:
             out = torch.empty((M, N), dtype=want, device=w.device)
         elif out.dtype != want or tuple(out.shape) != (M, N):
             raise KernelError(f"gemv_stream: out {tuple(out.shape)} {out.dtype} does not fit mode {mode}")
-    lib = _lib("gemv_stream.cu", STREAM_BUILD)
-    fuse = 1 if lazy else 2 if residual is not None else 0
-    _check(lib, lib.dk_gemv_stream(None if lazy else _p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, fuse,
-                                   _p(x.h) if lazy else None, _p(x.sq) if lazy else None, x.sq.shape[0] if lazy else 0,
-                                   _p(x.weight) if lazy else None, c_float(x.eps if lazy else 0.0), _p(residual), _p(sq),
-                                   _p(counters), _p(prefetch),
-                                   c_longlong(0 if prefetch is None else prefetch.numel() * prefetch.element_size()),
-                                   _stream()), "gemv_stream")
-    if residual is not None:
-        return Added(residual, sq)
+    lib = _lib("gemv_stream.cu")
+    _check(lib, lib.dk_gemv_stream(_p(x), _p(w), _p(out), _p(ws), M, N, K, mode, sk, blocks, warps, _stream()), "gemv_stream")
     return Partial(ws) if sk > 1 else out
-
-
-# ------------------------------------------------------------------------------ fused decode mixer
-def attention_decode_fused(qkv, out, q_norm_w, k_norm_w, cos, sin, eps, k_store, v_store, row_pos, page_table, n_heads,
-                           n_kv_heads, head_dim, window, scale, nsplit, ws_acc, ws_ml, write_kv=True):
-    """A decode step's attention from the projection row (``qkv``: bf16 tensor or ``Partial``): the
-    attention kernel itself applies the per-head norm and the rotation to the new token's q and k
-    and writes the new key and value to the cache (unless ``write_kv`` is false), so the separate
-    kernel for that is not launched. Splits, scratch and merge as for ``attention_decode_bf16``."""
-    n_seq, width = qkv.shape[0], qkv.shape[1]
-    qkv, parts, n_parts, stride = _parts(qkv)
-    _need(qkv, "qkv", torch.bfloat16, 2), _need(out, "out", torch.bfloat16, 2)
-    _need(q_norm_w, "q_norm_w", torch.float32, 1), _need(k_norm_w, "k_norm_w", torch.float32, 1)
-    _need(cos, "cos", torch.float32, 2), _need(sin, "sin", torch.float32, 2)
-    _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
-    _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
-    if width != (n_heads + 2 * n_kv_heads) * head_dim:
-        raise KernelError(f"qkv width {width} != (nh + 2 nkv) * hd")
-    if not 1 <= nsplit <= 16:
-        raise KernelError(f"attention_decode_fused: {nsplit} splits, the merge takes 1 to 16")
-    if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * 4 * nsplit * head_dim \
-            or ws_ml.numel() < n_seq * n_heads * 4 * nsplit * 2:
-        raise KernelError("attention_decode_fused: scratch too small for this batch and split count")
-    lib = _attn_lib(head_dim)
-    _check(lib, lib.dk_attn_decode_fused(_p(qkv), parts, n_parts, stride, _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin),
-                                         c_float(eps), _p(out), _p(ws_acc), _p(ws_ml), _p(k_store), _p(v_store),
-                                         _p(row_pos), _p(page_table), page_table.shape[1], n_seq, n_heads, n_kv_heads,
-                                         int(window or 0), c_float(scale), nsplit, int(bool(write_kv)), _stream()),
-           "attention_decode_fused", 2)
 
 
 # ------------------------------------------------------------- tensor-core product for many rows
@@ -602,20 +499,21 @@ def skinny_tc_plan(M, N, K, mode, allow_partial=False):
     block per unit (tile, slice), as many units as fit the SMs, slices of at least 8 blocks of 64
     columns (fewer cannot keep the load ring busy), fewer slices on a tie."""
     kb = (K + 63) // 64
+    sms = sm_count()
     if mode == MODE_SILU:      # no slices (SiLU needs whole sums): the tile width that covers most SMs
         def fill(bn):
             tiles = (N + bn // 2 - 1) // (bn // 2)
-            return tiles / (-(-tiles // SM_COUNT) * SM_COUNT)
+            return tiles / (-(-tiles // sms) * sms)
         return max((256, 192, 160, 144, 128), key=fill), 1
     if mode != MODE_STORE or not allow_partial:
         return 256, 1
     best = None
     for bn in (256, 128):
         tiles = (N + bn - 1) // bn
-        sk = max(1, min(SM_COUNT // tiles, kb // 8))
+        sk = max(1, min(sms // tiles, kb // 8))
         while sk > 1 and (sk - 1) * ((kb + sk - 1) // sk) >= kb:
             sk -= 1
-        key = (min(tiles * sk, SM_COUNT), -sk)
+        key = (min(tiles * sk, sms), -sk)
         if best is None or key > best[0]:
             best = (key, (bn, sk))
     return best[1]
@@ -625,8 +523,8 @@ def gemm_tc_fills_gpu(M, N, min_fill=0.8):
     """Whether gemm_tc's 128 x 256 output tiles, one persistent block per SM, keep the last wave
     at least ``min_fill`` full on average; below that the library's smaller tiles win."""
     tiles = ((M + 127) // 128) * ((N + 255) // 256)
-    waves = tiles / SM_COUNT
-    return waves / -(-tiles // SM_COUNT) >= min_fill
+    waves = tiles / sm_count()
+    return waves / -(-tiles // sm_count()) >= min_fill
 
 
 def gemm_tc_check():
@@ -643,11 +541,6 @@ def gemm_tc_check():
 # --------------------------------------------------------------- tensor-core prefill attention
 TC_ATTENTION_HEAD_DIMS = (64, 128)
 TC_TILE_ROWS = 128
-# Keys a step of the kernel takes, 64 or 128 (a build option of attention_tc.cu). 64: two blocks an SM,
-# two softmax threads a query row. 128: one block an SM with all of its tensor memory, four threads a
-# row, half as many S instructions. Measured on B200, 32 heads of 128: 12.4 / 50.2 / 518 us at 512 /
-# 2,048 / 8,192 tokens with 64, 11.3 / 53.2 / 564 us with 128.
-TC_ATTENTION_STEP_KEYS = 64
 _attn_sched = {}
 
 
@@ -667,29 +560,8 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
     sched = _attn_sched.get(stream)          # the kernel's work counter: launches of one stream share it, in turn
     if sched is None:
         sched = _attn_sched[stream] = torch.zeros(2, dtype=torch.int32, device=q.device)
-    lib = _lib("attention_tc.cu", {"HD": head_dim, "STEP_KEYS": TC_ATTENTION_STEP_KEYS})
+    lib = _lib("attention_tc.cu", {"HD": head_dim})
     _check(lib, lib.dk_attn_prefill_tc(_p(q), _p(out), _p(k_store), _p(v_store), c_longlong(q.shape[0]),
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
                                        c_float(scale), _p(_tc_err), _p(sched), c_void_p(stream)), "attention_prefill_tc")
-
-
-def kernel_trace():
-    """Development (needs DRYFT_KERNEL_TRACE=1 in the environment before the first import): the
-    notes the kernels launched since the last call left, as a time-ordered list of
-    (nanoseconds, source file, blocks, threads per block); each is the moment the kernel's wait for
-    its predecessor ended."""
-    import ctypes
-
-    from . import build
-    if not build.TRACE:
-        raise KernelError("kernel_trace: set DRYFT_KERNEL_TRACE=1 before importing the package")
-    events = []
-    for (source, _), lib in build.loaded_libs().items():
-        if not hasattr(lib, "dk_trace_read"):
-            continue
-        t = (ctypes.c_ulonglong * 8192)()
-        sig = (ctypes.c_ulonglong * 8192)()
-        n = lib.dk_trace_read(t, sig, 8192)
-        events += [(t[i], source, sig[i] >> 32, sig[i] & 0xffffffff) for i in range(max(0, n))]
-    return sorted(events)

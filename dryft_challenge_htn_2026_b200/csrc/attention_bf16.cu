@@ -439,284 +439,3 @@ DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float
     return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
                      (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh);
 }
-
-// ------------------------------------------------------------------------------- fused decode
-// attn_decode_kernel with the work of the kernel before it taken in: per-head RMSNorm and rotation
-// of the new token's q and k, and the cache write. grid (nsplit, nkv * mtiles, sequences), the
-// warps' rings, the partial results and the merge kernel as there.
-//  * The projection row qkv[b] = [q | k | v] comes as a bf16 tensor or as n_parts float32 partial
-//    sums parts[k][b][width]. Every lane fetches the elements of its own mma fragment of q: the
-//    elements of a row lie in the four lanes of a group, and an element and its rotation partner
-//    half a head further lie in the same lane, so norm and rotation need two shuffles and no
-//    shared memory.
-//  * No page is written by the kernel before this one, so the whole ring is requested before the
-//    wait for it. The new token's row of its page does not exist in memory yet: the warp that owns
-//    that row computes the new key and value, puts them into its landed copy of the page, and, in
-//    the block of the first head tile, into the cache (write_kv != 0; a layer that reads another
-//    layer's cache finds the row there).
-template <int D>
-__global__ void __launch_bounds__(128, D == 2 ? 3 : 2)
-attn_decode_fused_kernel(const bf16* qkv, const float* parts, int n_parts, size_t part_stride, const float* __restrict__ qn,
-                         const float* __restrict__ kn, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                         float eps, float* ws_acc, float* ws_ml, bf16* k_store, bf16* v_store, const int* row_pos,
-                         const int* page_table, int pt_stride, int nh, int nkv, int window, float sl2, int write_kv) {
-    extern __shared__ __align__(16) bf16 smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int G = nh / nkv, mtiles = (G + 15) / 16;
-    const int split = blockIdx.x, nsplit = gridDim.x;
-    const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
-    const int b = blockIdx.z;
-    const int head0 = kvh * G + mt * 16;
-    const int heads_here = min(16, G - mt * 16);
-    constexpr int CHUNK = 2 * 16 * KSTR;
-    constexpr int CPR = HD / 8;
-    constexpr int UNITS = HD / 8;             // a lane holds columns 8u + 2t, 8u + 2t + 1 of its rows
-    constexpr int HALF = HD / 2;
-    constexpr int NP = (HALF + 31) / 32;      // pairs (d, d + HALF) a lane of the key's warp holds
-    bf16* ring = smem + warp * D * CHUNK;
-    const int pos = row_pos[b];
-    const int* pt = page_table + (size_t)b * pt_stride;
-    const int key_lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
-    const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
-    const int jt0 = t_lo + split * per, jt1 = pos >= 0 ? min(t_hi + 1, jt0 + per) : jt0;  // [jt0, jt1)
-    auto fetch = [&](int jt, int slot) {
-        const size_t off = kv_offset(pt[jt], nkv, kvh, warp * 16, HD);
-        bf16* dst = ring + slot * CHUNK;
-        for (int c = lane; c < 16 * CPR; c += 32) {
-            const int row = c / CPR, col = (c % CPR) * 8;
-            cp_async16(dst + row * KSTR + col, k_store + off + (size_t)row * HD + col);
-            cp_async16(dst + 16 * KSTR + row * KSTR + col, v_store + off + (size_t)row * HD + col);
-        }
-    };
-    for (int i = 0; i < D; i++) {             // chunk i is commit group i
-        if (jt0 + i < jt1) fetch(jt0 + i, i);
-        cp_async_commit();
-    }
-    // the warp whose 16 keys of the newest page include the new token
-    const bool has_new = write_kv && jt0 <= t_hi && t_hi < jt1 && warp == (pos % DK_PAGE) / 16;
-    // norm weights and angles: in fragment order for q, in lane order for the new key
-    float2 wq[UNITS], cs[UNITS / 2], sn[UNITS / 2];
-    const bool work = jt0 < jt1;
-#pragma unroll
-    for (int u = 0; u < UNITS; u++)
-        wq[u] = work && qn ? *reinterpret_cast<const float2*>(qn + 8 * u + 2 * t) : make_float2(1.f, 1.f);
-#pragma unroll
-    for (int u = 0; u < UNITS / 2; u++) {
-        const size_t at = (size_t)max(pos, 0) * HALF + 8 * u + 2 * t;
-        cs[u] = work && cos_t ? *reinterpret_cast<const float2*>(cos_t + at) : make_float2(1.f, 1.f);
-        sn[u] = work && cos_t ? *reinterpret_cast<const float2*>(sin_t + at) : make_float2(0.f, 0.f);
-    }
-    float kc[NP], ks_[NP], kw1[NP], kw2[NP];
-#pragma unroll
-    for (int i = 0; i < NP; i++) {
-        const int d = lane + 32 * i;
-        const bool on = has_new && d < HALF;
-        kc[i] = on && cos_t ? cos_t[(size_t)pos * HALF + d] : 1.f;
-        ks_[i] = on && cos_t ? sin_t[(size_t)pos * HALF + d] : 0.f;
-        kw1[i] = on && kn ? kn[d] : 1.f;
-        kw2[i] = on && kn ? kn[d + HALF] : 1.f;
-    }
-    pdl_wait();
-    pdl_launch_dependents();
-
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float acc[HD / 8][4];
-    if (work) {
-        const size_t width = (size_t)(nh + 2 * nkv) * HD;
-        // ---- the new key and value, by the warp that owns their row
-        float k1[NP], k2[NP], v1[NP], v2[NP];
-        if (has_new) {
-            const size_t k_at = (size_t)b * width + (size_t)(nh + kvh) * HD, v_at = k_at + (size_t)nkv * HD;
-#pragma unroll
-            for (int i = 0; i < NP; i++) k1[i] = k2[i] = v1[i] = v2[i] = 0.f;
-            if (parts == nullptr) {
-#pragma unroll
-                for (int i = 0; i < NP; i++) {
-                    const int d = lane + 32 * i;
-                    if (d < HALF) {
-                        k1[i] = __bfloat162float(qkv[k_at + d]), k2[i] = __bfloat162float(qkv[k_at + d + HALF]);
-                        v1[i] = __bfloat162float(qkv[v_at + d]), v2[i] = __bfloat162float(qkv[v_at + d + HALF]);
-                    }
-                }
-            } else {
-#pragma unroll 2
-                for (int k = 0; k < n_parts; k++) {
-                    const float* pk = parts + (size_t)k * part_stride;
-#pragma unroll
-                    for (int i = 0; i < NP; i++) {
-                        const int d = lane + 32 * i;
-                        if (d < HALF) {
-                            k1[i] += pk[k_at + d], k2[i] += pk[k_at + d + HALF];
-                            v1[i] += pk[v_at + d], v2[i] += pk[v_at + d + HALF];
-                        }
-                    }
-                }
-            }
-        }
-        // ---- q of this block's heads, in fragment order: x[r][u] = row g + 8r, columns 8u + 2t, + 1
-        float2 x[2][UNITS];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const bool on = g + 8 * r < heads_here;
-            const size_t at = (size_t)b * width + (size_t)(head0 + g + 8 * r) * HD + 2 * t;
-#pragma unroll
-            for (int u = 0; u < UNITS; u++) x[r][u] = make_float2(0.f, 0.f);
-            if (!on) continue;
-            if (parts == nullptr) {
-#pragma unroll
-                for (int u = 0; u < UNITS; u++)
-                    x[r][u] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qkv + at + 8 * u));
-            } else {
-#pragma unroll 2
-                for (int k = 0; k < n_parts; k++) {
-                    const float* pk = parts + (size_t)k * part_stride + at;
-#pragma unroll
-                    for (int u = 0; u < UNITS; u++) {
-                        const float2 v = *reinterpret_cast<const float2*>(pk + 8 * u);
-                        x[r][u].x += v.x, x[r][u].y += v.y;
-                    }
-                }
-            }
-        }
-        if (has_new) {
-            if (kn) {
-                float ss = 0.f;
-#pragma unroll
-                for (int i = 0; i < NP; i++) ss += k1[i] * k1[i] + k2[i] * k2[i];
-                ss = warp_sum(ss);
-                const float rs = rsqrtf(ss / (float)HD + eps);
-#pragma unroll
-                for (int i = 0; i < NP; i++) k1[i] = k1[i] * rs * kw1[i], k2[i] = k2[i] * rs * kw2[i];
-            }
-            if (cos_t) {
-#pragma unroll
-                for (int i = 0; i < NP; i++) {
-                    const float a = k1[i], c = k2[i];
-                    k1[i] = a * kc[i] - c * ks_[i];
-                    k2[i] = c * kc[i] + a * ks_[i];
-                }
-            }
-            if (mt == 0) {
-                const size_t off = kv_offset(pt[t_hi], nkv, kvh, pos % DK_PAGE, HD);
-#pragma unroll
-                for (int i = 0; i < NP; i++) {
-                    const int d = lane + 32 * i;
-                    if (d < HALF) {
-                        k_store[off + d] = __float2bfloat16_rn(k1[i]), k_store[off + d + HALF] = __float2bfloat16_rn(k2[i]);
-                        v_store[off + d] = __float2bfloat16_rn(v1[i]), v_store[off + d + HALF] = __float2bfloat16_rn(v2[i]);
-                    }
-                }
-            }
-        }
-        uint32_t qf[HD / 16][4];
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-            if (qn) {
-                float ss = 0.f;
-#pragma unroll
-                for (int u = 0; u < UNITS; u++) ss += x[r][u].x * x[r][u].x + x[r][u].y * x[r][u].y;
-                ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-                ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-                const float rs = rsqrtf(ss / (float)HD + eps);
-#pragma unroll
-                for (int u = 0; u < UNITS; u++) x[r][u].x = x[r][u].x * rs * wq[u].x, x[r][u].y = x[r][u].y * rs * wq[u].y;
-            }
-            if (cos_t) {
-#pragma unroll
-                for (int u = 0; u < UNITS / 2; u++) {
-                    const float2 a = x[r][u], c = x[r][u + UNITS / 2];
-                    x[r][u] = make_float2(a.x * cs[u].x - c.x * sn[u].x, a.y * cs[u].y - c.y * sn[u].y);
-                    x[r][u + UNITS / 2] = make_float2(c.x * cs[u].x + a.x * sn[u].x, c.y * cs[u].y + a.y * sn[u].y);
-                }
-            }
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ks++) {
-                qf[ks][r] = pack_bf16(x[r][2 * ks].x, x[r][2 * ks].y);
-                qf[ks][2 + r] = pack_bf16(x[r][2 * ks + 1].x, x[r][2 * ks + 1].y);
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-        const int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
-        for (int jt = jt0; jt < jt1; jt++) {
-            const int slot = (jt - jt0) % D;
-            cp_async_wait<D - 1>();           // this warp's chunk jt has landed
-            __syncwarp();
-            bf16* Ks = ring + slot * CHUNK;
-            if (has_new && jt == t_hi) {      // the new token's row, which memory does not hold yet
-                bf16* kr = Ks + (pos % 16) * KSTR;
-                bf16* vr = kr + 16 * KSTR;
-#pragma unroll
-                for (int i = 0; i < NP; i++) {
-                    const int d = lane + 32 * i;
-                    if (d < HALF) {
-                        kr[d] = __float2bfloat16_rn(k1[i]), kr[d + HALF] = __float2bfloat16_rn(k2[i]);
-                        vr[d] = __float2bfloat16_rn(v1[i]), vr[d + HALF] = __float2bfloat16_rn(v2[i]);
-                    }
-                }
-                __syncwarp();
-            }
-            const int key0 = jt * DK_PAGE + warp * 16;
-            if (key0 <= pos && key0 + 15 >= key_lo)
-                warp_attend<16>(qf, Ks, Ks + 16 * KSTR, key0, lo, hi, sl2, m, l, acc);
-            __syncwarp();                     // every lane is done reading the slot before it is refilled
-            if (jt + D < jt1) fetch(jt + D, slot);
-            cp_async_commit();
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < HD / 8; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    }
-    cp_async_wait<0>();
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
-    const int n_parts_out = 4 * nsplit, part = 4 * split + warp;
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-        const int row = g + 8 * r;
-        if (row < heads_here) {
-            const size_t at = ((size_t)b * nh + head0 + row) * n_parts_out + part;
-            float* dst = ws_acc + at * HD + 2 * t;
-#pragma unroll
-            for (int nt = 0; nt < HD / 8; nt++) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(acc[nt][2 * r], acc[nt][2 * r + 1]);
-            if (t == 0) *reinterpret_cast<float2*>(ws_ml + at * 2) = make_float2(m[r], l[r]);
-        }
-    }
-}
-
-// As dk_attn_decode_bf16, from the projection row (bf16 tensor qkv, or n_parts float32 partial sums
-// parts[k][n_seq][width], part_stride floats apart): norm weights qn, kn [HD] or null, angle tables
-// cos_t, sin_t [positions][HD / 2] or null.
-DK_EXPORT int dk_attn_decode_fused(const void* qkv, const float* parts, int n_parts, long long part_stride, const float* qn,
-                                   const float* kn, const float* cos_t, const float* sin_t, float eps, void* out,
-                                   float* ws_acc, float* ws_ml, void* k_store, void* v_store, const int* row_pos,
-                                   const int* page_table, int pt_stride, int n_seq, int nh, int nkv, int window,
-                                   float scale, int nsplit, int write_kv, cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1 || nsplit > 16 || ws_acc == nullptr || ws_ml == nullptr) return (int)cudaErrorInvalidValue;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(2));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attn_decode_fused_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem(3));
-        if (e != cudaSuccess) return (int)e;
-        attr_done = true;
-    }
-    const int G = nh / nkv, mtiles = (G + 15) / 16;
-    const dim3 grid(nsplit, nkv * mtiles, n_seq);
-    int e;
-    if (decode_ring_depth((long long)nsplit * nkv * mtiles * n_seq) == 3)
-        e = dk_launch(attn_decode_fused_kernel<3>, grid, dim3(128), decode_smem(3), st, (const bf16*)qkv, parts, n_parts,
-                      (size_t)part_stride, qn, kn, cos_t, sin_t, eps, ws_acc, ws_ml, (bf16*)k_store, (bf16*)v_store, row_pos,
-                      page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, write_kv);
-    else
-        e = dk_launch(attn_decode_fused_kernel<2>, grid, dim3(128), decode_smem(2), st, (const bf16*)qkv, parts, n_parts,
-                      (size_t)part_stride, qn, kn, cos_t, sin_t, eps, ws_acc, ws_ml, (bf16*)k_store, (bf16*)v_store, row_pos,
-                      page_table, pt_stride, nh, nkv, window, scale * 1.4426950408889634f, write_kv);
-    if (e) return e;
-    return dk_launch(attn_combine_kernel, dim3((n_seq * nh + 3) / 4), dim3(128), 0, st, (const float*)ws_acc,
-                     (const float*)ws_ml, (bf16*)out, 4 * nsplit, n_seq * nh);
-}

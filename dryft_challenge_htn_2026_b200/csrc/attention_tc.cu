@@ -1,10 +1,9 @@
 // Prefill attention on the 5th-generation tensor cores: ragged causal grouped-query flash
 // attention over the paged cache with S = Q.K^T and O += P.V as tcgen05.mma, accumulators in
-// tensor memory, tiles fed by TMA. Built per head size with -DHD=64 or -DHD=128, and with
-// -DSTEP_KEYS=64 (what is described below) or 128: steps of two pages, S buffers of 128 columns, four
-// softmax threads a row (warps 0-15), one block an SM holding all 512 columns of its tensor memory.
-// The latter halves the instructions of S but has no second block to fill its gaps; measured slower
-// from 2,048 tokens on (53 vs 50 us, 564 vs 518 us at 8,192), faster at 512 (11.3 vs 12.4 us).
+// tensor memory, tiles fed by TMA. Built per head size with -DHD=64 or -DHD=128. (Steps of two pages
+// with S buffers of 128 columns, four softmax threads a row and one block an SM holding all 512
+// columns of its tensor memory halve the instructions of S but leave no second block to fill the
+// gaps: measured slower from 2,048 tokens on, 53 vs 50 us, 564 vs 518 us at 8,192.)
 // Formulas as attention_bf16.cu (reference: engine/fused.py:301-343): scores scaled by
 // scale*log2(e), running maximum and sum in float32, P rounded to bfloat16 before P.V.
 //
@@ -44,34 +43,9 @@
 #endif
 static_assert(HD == 64 || HD == 128, "tensor-core prefill attention is built for head sizes 64 and 128");
 
-// Development only (-DATTN_TRACE): clock stamps of the first steps of one block's roles, and for
-// every (tile, head) item its start and end on the global timer, its SM and its number of steps;
-// read back with dk_attn_trace*. This is how the empty block slots and the idle mma thread were found.
-#ifdef ATTN_TRACE
-__device__ long long g_trace[512];
-#define TRACE(slot) do { if (blockIdx.x == 0 && items == 0 && i < 6) g_trace[(slot) + 16 * i] = clock64(); } while (0)
-DK_EXPORT int dk_attn_trace(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace)); }
-// per block: start and end on the global timer (ns), SM, steps
-__device__ long long g_blocks[4 * 4096];
-__device__ long long g_clk[2 * 4096];
-DK_EXPORT int dk_attn_trace_clk(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_clk, sizeof(g_clk)); }
-DK_EXPORT int dk_attn_trace_blocks(long long* host) { return (int)cudaMemcpyFromSymbol(host, g_blocks, sizeof(g_blocks)); }
-__device__ __forceinline__ long long trace_now() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#else
-#define TRACE(slot)
-#endif
-
 namespace {
 
-#ifndef STEP_KEYS
-#define STEP_KEYS 64
-#endif
-constexpr int BM = 128, BN = STEP_KEYS;           // queries per block, keys per step (one or two cache pages)
-static_assert(BN == DK_PAGE || BN == 2 * DK_PAGE, "a step is one or two pages of the cache");
+constexpr int BM = 128, BN = DK_PAGE;             // queries per block, keys per step (one cache page)
 constexpr int PAGES = BN / DK_PAGE;
 constexpr int TPR = BN / 32;                      // softmax threads per query row: 32 key columns each
 constexpr int SOFT = 128 * TPR;                   // softmax threads; then the mma warp, then the loader warp
@@ -308,13 +282,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const Item cur = item_of(item);
     const int h = cur.h, rows_here = cur.rows_here, flat0 = cur.flat0, min_pos = cur.min_pos, pos0 = cur.pos0, q0 = cur.q0;
     const int blk_lo = cur.blk_lo, n_blk = cur.n_blk;
-#ifdef ATTN_TRACE
-    if (threadIdx.x == 0 && item < 4096) {
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        g_blocks[4 * item] = trace_now(), g_blocks[4 * item + 2] = smid, g_blocks[4 * item + 3] = n_blk, g_clk[2 * item] = clock64();
-    }
-#endif
 
     // Step j of the item is step t = step + j of the block; it uses stage / buffer / barrier t & 1, whose
     // barriers are then in their phase (t >> 1) & 1.
@@ -368,27 +335,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             for (int i = 0; i < n_blk && ok; i++) {
                 const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
-                TRACE(0);
                 if (i + 1 < n_blk) {                        // S of the next step, while the softmax warps work on this one
                     const uint32_t tn = t + 1;
                     if (!mbar_wait(bar_k + (tn & 1), (tn >> 1) & 1)) { ok = false; break; }
-                    TRACE(1);
                     // its buffer held P of the step before this one: P.V of that step must be done with it
                     if (i >= 1 && !mbar_wait(bar_o + (tn & 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
                     fence_after();
                     issue_s(i + 1);
-                    TRACE(2);
                 }
                 if (!mbar_wait(bar_p + b, ph)) { ok = false; break; }
-                TRACE(4);
                 if (!mbar_wait(bar_v + b, ph)) { ok = false; break; }   // P is written, V is here
-                TRACE(5);
                 fence_after();
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++)
                     umma_ts(t_o, t_s + b * BN + k * 8, dv + (uint64_t)((b * KV_BYTES + k * 16 * 128) >> 4), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
                 umma_commit(bar_o + b);
-                TRACE(6);
             }
             if (!ok) atomicExch(err, 1), item_slot[1] = 1;
         }
@@ -404,14 +365,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int i = 0; i < n_blk && ok; i++) {
             const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
             const int key0 = (blk_lo + i) * BN + col0;
-            if (threadIdx.x == 0) TRACE(8);
             if (!mbar_wait(bar_s + b, ph)) { ok = false; break; }
-            if (threadIdx.x == 0) TRACE(9);
             fence_after();
             uint32_t v[32];
             tmem_ld32(t_s + lane_off + b * BN + col0, v);
             tmem_wait_ld();
-            if (threadIdx.x == 0) TRACE(10);
             // every key of the step visible to every row of the tile: no per-element test
             const bool open = window <= 0 && (blk_lo + i) * BN + BN - 1 <= min_pos;
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -431,9 +389,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             // the row's maximum is over both threads of the row; once both have been here, both have read their S
             // (P of one goes over columns of S that the other reads)
             xch[(i & 1) * SOFT + threadIdx.x] = mx;
-            if (threadIdx.x == 0) TRACE(7);
             asm volatile("bar.sync %0, %1;" ::"r"(1 + ((threadIdx.x >> 5) & 3)), "n"(32 * TPR) : "memory");   // the warps that share these rows
-            if (threadIdx.x == 0) TRACE(3);
             float m_new = fmaxf(m, mx);
 #pragma unroll
             for (int o = 1; o < TPR; o++) m_new = fmaxf(m_new, xch[(i & 1) * SOFT + ((threadIdx.x + 128 * o) & (SOFT - 1))]);
@@ -457,7 +413,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tmem_st_o(t_o + lane_off + c, o);
                 }
             }
-            if (threadIdx.x == 0) TRACE(11);
             // P = exp2(S * sl2 - m), its sum, and P as bfloat16 over the first columns of this S buffer
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t p[16];
@@ -471,11 +426,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_st16(t_s + lane_off + b * BN + col0 / 2, p);
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m = m_new;
-            if (threadIdx.x == 0) TRACE(12);
             tmem_wait_st();
             fence_before();
             mbar_arrive(bar_p + b);
-            if (threadIdx.x == 0) TRACE(13);
         }
         if (ok) ok = mbar_wait(bar_o + ((step + n_blk - 1) & 1), ((step + n_blk - 1) >> 1) & 1);
         // the row's sum is over both threads of the row
@@ -513,9 +466,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     fence_before();
     __syncthreads();
     fence_after();
-#ifdef ATTN_TRACE
-    if (threadIdx.x == 0 && item < 4096) g_blocks[4 * item + 1] = trace_now(), g_clk[2 * item + 1] = clock64();
-#endif
     }
     pdl_launch_dependents();
     if (threadIdx.x == 0 && atomicAdd(&sched[1], 1) == (int)gridDim.x - 1) sched[0] = 0, sched[1] = 0;   // the last block leaves zeros for the next launch

@@ -19,11 +19,6 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 BUILD_DIR = os.path.join(HERE, "_build")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
-# development: DRYFT_KERNEL_TRACE=1 builds (separately named) objects whose kernels note when they
-# start; csrc.api.kernel_trace() reads the notes
-TRACE = os.environ.get("DRYFT_KERNEL_TRACE", "") not in ("", "0")
-if TRACE:
-    NVCC_FLAGS.append("-DDK_TRACE")
 
 _libs = {}
 _lock = threading.Lock()
@@ -131,6 +126,6 @@ def build_all(head_dims=(16, 32, 64, 128), verbose=False):
             ("gemm_tc.cu", None), ("sampling.cu", None),
             ("sample_noalloc.cu", None)]
     jobs += [("attention_bf16.cu", {"HD": hd}) for hd in head_dims]
-    jobs += [("attention_tc.cu", {"HD": hd, "STEP_KEYS": 64}) for hd in head_dims if hd in (64, 128)]
+    jobs += [("attention_tc.cu", {"HD": hd}) for hd in head_dims if hd in (64, 128)]
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
         return list(ex.map(lambda j: compile_lib(j[0], j[1], verbose), jobs))

@@ -53,44 +53,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // predecessor in the stream drains; pdl_wait() blocks until the predecessor has finished and its
 // writes are visible, so nothing the predecessor (or any earlier kernel) wrote may be read, and
 // nothing may be written, before it. Without the attribute both are no-ops.
-#ifdef DK_TRACE
-// Development timeline (built only with -DDK_TRACE): the first thread of every launch notes the
-// global timer when its wait for the previous kernel ends, with its grid and block size. The gaps
-// between consecutive notes are the times the kernels take inside a stream or graph, overlap
-// included. One buffer per shared object; dk_trace_read copies it out and empties it.
-#define DK_TRACE_MAX 8192
-__device__ unsigned long long dk_trace_t[DK_TRACE_MAX];
-__device__ unsigned long long dk_trace_sig[DK_TRACE_MAX];
-__device__ unsigned int dk_trace_n;
-__device__ __forceinline__ void dk_trace_note() {
-    if ((threadIdx.x | threadIdx.y | blockIdx.x | blockIdx.y | blockIdx.z) == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        const unsigned int i = atomicAdd(&dk_trace_n, 1u);
-        if (i < DK_TRACE_MAX) {
-            dk_trace_t[i] = t;
-            dk_trace_sig[i] = ((unsigned long long)(gridDim.x * gridDim.y * gridDim.z) << 32) | (blockDim.x * blockDim.y);
-        }
-    }
-}
-extern "C" __attribute__((visibility("default"))) int dk_trace_read(unsigned long long* t, unsigned long long* sig, int max) {
-    unsigned int n = 0, zero = 0;
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    cudaMemcpyFromSymbol(&n, dk_trace_n, sizeof(n));
-    if (n > (unsigned)max) n = max;
-    if (n > DK_TRACE_MAX) n = DK_TRACE_MAX;
-    cudaMemcpyFromSymbol(t, dk_trace_t, n * sizeof(unsigned long long));
-    cudaMemcpyFromSymbol(sig, dk_trace_sig, n * sizeof(unsigned long long));
-    cudaMemcpyToSymbol(dk_trace_n, &zero, sizeof(zero));
-    return (int)n;
-}
-__device__ __forceinline__ void pdl_wait() {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    dk_trace_note();
-}
-#else
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-#endif
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 static int g_pdl = 0;

@@ -146,8 +146,12 @@ __global__ void silu_mul_kernel(const T* gu, T* out, size_t n, int I) {
 // Tokens with position < 0 are padding: nothing is written for them.
 // With ``parts`` the projection row is the sum of n_parts float32 partial rows
 // parts[k][t][heads*hd] (split-K output of the skinny product) instead of qkv[t].
+// With ``dense_out`` every head (q, k and v) goes to its place in dense_out [T, heads*hd] instead,
+// and nothing else is written: the step between a norm and a position encoding that a part
+// applies itself before the cache is written.
 template <typename T>
 __global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int n_parts, size_t part_stride, T* q_out,
+                                          T* dense_out,
                                           const float* __restrict__ qn, const float* __restrict__ kn,
                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                           const int* row_pos, const int* row_seq,
@@ -165,10 +169,12 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int 
     const int pos = live ? row_pos[t] : -1;
     const int half = hd >> 1;
     const bool is_q = hidx < nh, is_v = hidx >= nh + nkv;
-    const bool work = pos >= 0 && (is_q || write_kv);
+    const bool work = pos >= 0 && (is_q || write_kv || dense_out != nullptr);
     T* dst = nullptr;
     if (work) {
-        if (is_q) {
+        if (dense_out != nullptr) {
+            dst = dense_out + ((size_t)t * heads + hidx) * hd;
+        } else if (is_q) {
             dst = q_out + ((size_t)t * nh + hidx) * hd;
         } else {
             const int kvh = (hidx - nh) % nkv;
@@ -389,7 +395,7 @@ add_rmsnorm_warp_kernel(float* h, const bf16* delta, const float* __restrict__ w
 // of GS lanes (GS = the power of two >= head_dim / 16) takes one (token, head); a warp takes 32 / GS
 // of them. Lane j of a group holds elements [8j, 8j+8) of each half of the head.
 template <int GS>
-__global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, const float* __restrict__ qn,
+__global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, bf16* dense_out, const float* __restrict__ qn,
                                                const float* __restrict__ kn, const float* __restrict__ cos_t,
                                                const float* __restrict__ sin_t, const int* row_pos, const int* row_seq,
                                                const int* page_table, int pt_stride, bf16* k_store, bf16* v_store,
@@ -404,11 +410,13 @@ __global__ void qk_norm_rope_write_wide_kernel(const bf16* qkv, bf16* q_out, con
     const int pos = live ? row_pos[t] : -1;
     const int half = hd >> 1, half8 = hd >> 4;
     const bool is_v = hidx >= nh + nkv;
-    const bool work = pos >= 0 && (hidx < nh || write_kv);
+    const bool work = pos >= 0 && (hidx < nh || write_kv || dense_out != nullptr);
     const bf16* x = qkv + (size_t)t * heads * hd + (size_t)hidx * hd;
     bf16* dst = nullptr;
     if (work) {
-        if (hidx < nh) {
+        if (dense_out != nullptr) {
+            dst = dense_out + ((size_t)t * heads + hidx) * hd;
+        } else if (hidx < nh) {
             dst = q_out + ((size_t)t * nh + hidx) * hd;
         } else {
             const int kvh = (hidx - nh) % nkv;
@@ -516,7 +524,7 @@ DK_EXPORT int dk_silu_mul(int dtype, const void* gu, void* out, long long n_rows
 }
 
 DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* parts, int n_parts, long long part_stride,
-                                    void* q_out, const float* qn, const float* kn,
+                                    void* q_out, void* dense_out, const float* qn, const float* kn,
                                     const float* cos_t, const float* sin_t, const int* row_pos, const int* row_seq,
                                     const int* page_table, int pt_stride, void* k_store, void* v_store, int n_tok,
                                     int nh, int nkv, int hd, float eps, int write_kv, cudaStream_t st) {
@@ -529,7 +537,7 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* par
         const unsigned wblocks = (unsigned)((warps + 4LL * (32 / gs) - 1) / (4LL * (32 / gs)));
 #define ROPE_WIDE(GS)                                                                                                  \
     return dk_launch(qk_norm_rope_write_wide_kernel<GS>, dim3(wblocks), dim3(128), 0, st, (const bf16*)qkv, (bf16*)q_out, \
-                     qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride, (bf16*)k_store, (bf16*)v_store, n_tok, \
+                     (bf16*)dense_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride, (bf16*)k_store, (bf16*)v_store, n_tok, \
                      nh, nkv, hd, eps, write_kv)
         if (gs == 1) ROPE_WIDE(1);
         if (gs == 2) ROPE_WIDE(2);
@@ -539,32 +547,10 @@ DK_EXPORT int dk_qk_norm_rope_write(int dtype, const void* qkv, const float* par
 #undef ROPE_WIDE
     }
     DISPATCH_T(dtype, return dk_launch(qk_norm_rope_write_kernel<T>, dim3(blocks), dim3(128), 0, st, (const T*)qkv,
-                                       parts, n_parts, (size_t)part_stride, (T*)q_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
+                                       parts, n_parts, (size_t)part_stride, (T*)q_out, (T*)dense_out, qn, kn, cos_t, sin_t, row_pos, row_seq, page_table, pt_stride,
                                        (T*)k_store, (T*)v_store, n_tok, nh, nkv, hd, eps, write_kv));
 }
 
 DK_EXPORT int dk_gather_rows_f32(const float* src, const int* rows, float* out, int n_rows, int H, cudaStream_t st) {
     return dk_launch(gather_rows_f32_kernel, dim3(n_rows), dim3(256), 0, st, src, rows, out, H);
-}
-
-// ---------------------------------------------------------------------------------------------
-// Asks the memory system to bring [p, p + bytes) into L2 (a hint; nothing is read into the SM).
-// Launched beside small latency-bound kernels of the decode step so that HBM keeps streaming the
-// next weight matrix while they run.
-__global__ void l2_prefetch_kernel(const char* p, size_t bytes, size_t piece) {
-    const size_t n = (bytes + piece - 1) / piece;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t off = i * piece;
-        const unsigned sz = (unsigned)(bytes - off < piece ? (bytes - off) & ~(size_t)15 : piece);
-        if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"(sz) : "memory");
-    }
-}
-
-DK_EXPORT int dk_l2_prefetch(const void* p, long long bytes, cudaStream_t st) {
-    if (bytes <= 0) return 0;
-    const size_t piece = 16384;
-    size_t n = ((size_t)bytes + piece - 1) / piece;
-    unsigned blocks = (unsigned)((n + 127) / 128);
-    if (blocks > 148) blocks = 148;
-    return dk_launch(l2_prefetch_kernel, dim3(blocks), dim3(128), 0, st, (const char*)p, (size_t)bytes, piece);
 }

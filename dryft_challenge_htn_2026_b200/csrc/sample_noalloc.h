@@ -22,6 +22,10 @@
  *    overlap on the GPU (different streams, no ordering between them) would overwrite each other's
  *    partial results: keep calls on one device ordered.
  *  - It calls no cudaMalloc, cudaFree or any other allocating routine.
+ *  - logits may have any alignment; rows that start on 16-byte boundaries (a 16-byte aligned
+ *    pointer and V a multiple of 4) are read with wider loads.
+ *  - Calls may follow one another on a stream on the same positions with advance != 0, also under
+ *    programmatic dependent launch: the position is read after the wait for the kernel before.
  *
  * Arguments are those of dk_sample without the two scratch pointers:
  *   logits [n_rows, V] float32, temperature [n_rows] float32 (0 = greedy), seeds [n_rows][2]

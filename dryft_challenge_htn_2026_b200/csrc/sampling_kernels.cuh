@@ -34,28 +34,33 @@ __global__ void sample_partial_kernel(const float* logits, int V, const float* t
                                       float* ws_val, int* ws_idx) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    // positions, temperatures and seeds are not written by the kernel before this one (the head):
-    // they are fetched before the wait for it
+    // temperatures and seeds are not written by the kernel before this one: they are fetched before
+    // the wait for it. The position is read after the wait, with the logits: the kernel before may be
+    // the one that advances it (two calls back to back on the same positions).
     const int b = blockIdx.y, chunk = blockIdx.x;
-    const int p = pos[rows ? rows[b] : b];
     const float temp = temperature[b];
     const uint32_t s_lo = seeds[2 * b], s_hi = seeds[2 * b + 1];
+    const int pos_at = rows ? rows[b] : b;
     pdl_wait();
     pdl_launch_dependents();
     const float* row = logits + (size_t)b * V;
     const int begin = chunk * SAMPLE_CHUNK, end = min(V, begin + SAMPLE_CHUNK);
     float bv = -INFINITY;
     int bi = begin;
+    // 16 logits a thread as four 16-byte loads where the rows are 16-byte aligned
+    const bool wide = V % 4 == 0 && blockDim.x * 16 == SAMPLE_CHUNK && ((uintptr_t)logits & 15) == 0;
+    float4 z4[4];
+    if (wide) {   // requested together, and together with the position, before any is looked at
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int i = begin + (k * (int)blockDim.x + (int)threadIdx.x) * 4;
+            z4[k] = i < end ? *reinterpret_cast<const float4*>(row + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+    }
+    const int p = pos[pos_at];
     if (p >= 0) {
         const float inv_t = temp > 0.f ? 1.f / temp : 1.f;
-        if (V % 4 == 0 && blockDim.x * 16 == SAMPLE_CHUNK) {
-            // 16 logits a thread, requested together as four 16-byte loads before any is looked at
-            float4 z4[4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const int i = begin + (k * (int)blockDim.x + (int)threadIdx.x) * 4;
-                z4[k] = i < end ? *reinterpret_cast<const float4*>(row + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-            }
+        if (wide) {
 #pragma unroll
             for (int k = 0; k < 4; k++) {
                 const int i = begin + (k * (int)blockDim.x + (int)threadIdx.x) * 4;

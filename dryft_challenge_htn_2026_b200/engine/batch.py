@@ -7,11 +7,6 @@ captured decode loop, kept in place and advanced by the kernels).
 import numpy as np
 import torch
 
-from ..csrc.api import PAGE
-
-TILE_ROWS = 64        # query rows per block of the mma.sync prefill attention kernel
-WIDE_TILE_ROWS = 128  # query rows per block of the tcgen05 prefill attention kernel
-
 
 class StepContext:
     """Fields:
@@ -26,14 +21,17 @@ class StepContext:
     seq_slot [n_seq]         cache slot of each sequence (row index into per-sequence state)
     seq_pos0 [n_seq]         tokens the sequence had cached before this step
     want_rows [n_want]       rows whose logits are returned, in request order
-    tiles [n_tiles, 2]       (sequence, first query) of each 64-row attention tile, heaviest first
-    tiles_wide [n, 2]        the same for 128-row tiles
     tables[g] [n_seq, P_g]   page ids of each sequence in cache group g
-    host                     dict of the same arrays as numpy, for parts that plan on the host
+    plans[key]               what the parts' ``StepPlan`` objects built for this step (e.g. the
+                             attention kernels' query tiles), on the device
+    host                     dict of the same arrays as numpy, for parts that plan on the host; None
+                             in a captured decode loop, whose positions advance on the device
     """
 
     def __init__(self, scratch_store=None):
         self._scratch = scratch_store if scratch_store is not None else {}
+        self.plans = {}
+        self.host = None
 
     def scratch(self, key, make):
         """A buffer (or tuple of buffers) that lives as long as the runner and is reused by every
@@ -57,10 +55,11 @@ def _pack(arrays, device):
     return [dev[o:o + a.size].view(a.shape) for a, o in zip(arrays, offs)]
 
 
-def build_context(cache, entries, device, scratch_store=None, pad_to=None):
+def build_context(cache, entries, device, scratch_store=None, pad_to=None, plans=()):
     """``entries``: list of (slot, tokens, want) with ``want`` positions among these tokens.
     Reserves cache room for the new tokens. ``pad_to``: for decode steps, pad the batch with rows
-    of position -1 up to this many rows (a captured graph has a fixed size)."""
+    of position -1 up to this many rows (a captured graph has a fixed size). ``plans``: the
+    ``StepPlan`` objects of the model's parts; each is built once and uploaded with the rest."""
     n_seq = len(entries)
     lens = np.array([len(e[1]) for e in entries], dtype=np.int64)
     if n_seq == 0 or (lens < 1).any():
@@ -88,18 +87,6 @@ def build_context(cache, entries, device, scratch_store=None, pad_to=None):
         row_seq = np.concatenate([row_seq, np.zeros(pad, np.int64)])
         row_pos = np.concatenate([row_pos, -np.ones(pad, np.int64)])
         rows = pad_to
-    tiles = []
-    for i in range(n_seq):
-        for q0 in range(0, int(lens[i]), TILE_ROWS):
-            tiles.append((int(pos0[i]) + min(q0 + TILE_ROWS, int(lens[i])), i, q0))
-    tiles.sort(key=lambda t: -t[0])
-    tiles = np.array([(t[1], t[2]) for t in tiles], dtype=np.int32).reshape(-1, 2)
-    wide = []
-    for i in range(n_seq):
-        for q0 in range(0, int(lens[i]), WIDE_TILE_ROWS):
-            wide.append((int(pos0[i]) + min(q0 + WIDE_TILE_ROWS, int(lens[i])), i, q0))
-    wide.sort(key=lambda t: -t[0])
-    wide = np.array([(t[1], t[2]) for t in wide], dtype=np.int32).reshape(-1, 2)
     slots = [e[0] for e in entries]
     tables = []
     for g in range(len(cache.groups)):
@@ -108,14 +95,18 @@ def build_context(cache, entries, device, scratch_store=None, pad_to=None):
             t = np.concatenate([t, -np.ones((rows - n_seq, t.shape[1]), np.int32)])
         tables.append(t)
     i32 = lambda a: np.ascontiguousarray(a, dtype=np.int32)
-    arrays = [i32(tok), i32(row_seq), i32(row_pos), i32(cu), i32(slots), i32(pos0), i32(want), tiles, wide] + tables
-    dev = _pack(arrays, device)
+    by_key = {}
+    for p in plans:
+        if p.key not in by_key:
+            by_key[p.key] = i32(p.build(lens, pos0, is_decode))
+    fixed = [i32(tok), i32(row_seq), i32(row_pos), i32(cu), i32(slots), i32(pos0), i32(want)]
+    dev = _pack(fixed + tables + list(by_key.values()), device)
     ctx = StepContext(scratch_store)
     ctx.n_tok, ctx.n_seq, ctx.n_want, ctx.is_decode = rows, n_seq, len(want), is_decode
     ctx.max_position = int((pos0 + lens).max()) - 1
-    (ctx.tok, ctx.row_seq, ctx.row_pos, ctx.cu_q, ctx.seq_slot, ctx.seq_pos0, ctx.want_rows, ctx.tiles,
-     ctx.tiles_wide) = dev[:9]
-    ctx.tables = dev[9:]
+    ctx.tok, ctx.row_seq, ctx.row_pos, ctx.cu_q, ctx.seq_slot, ctx.seq_pos0, ctx.want_rows = dev[:7]
+    ctx.tables = dev[7:7 + len(tables)]
+    ctx.plans = dict(zip(by_key, dev[7 + len(tables):]))
     ctx.host = dict(lens=lens, pos0=pos0, cu_q=cu, slots=slots, row_seq=row_seq, row_pos=row_pos)
     if is_decode:
         ctx.n_seq = rows  # the decode kernels run one sequence per row, padding rows included

@@ -136,9 +136,15 @@ class DecodeState:
         ctx.tok, ctx.row_seq, ctx.row_pos, ctx.seq_slot = d["tok"], d["row_seq"], d["row_pos"], d["seq_slot"]
         ctx.want_rows = torch.arange(rows, dtype=torch.int32, device=dev)
         ctx.tables = [cut(self.dev, 6 + g, (rows, width)) for g in range(ng)]
-        ctx.cu_q = ctx.seq_pos0 = ctx.tiles = ctx.tiles_wide = None
-        ctx.host = None
+        # one token a sequence: row i is sequence i, and what it had cached before is its position
+        ctx.cu_q = torch.arange(rows + 1, dtype=torch.int32, device=dev)
+        ctx.seq_pos0 = ctx.row_pos
+        ctx.host = None                       # positions advance on the device: the host does not know them
         self.ctx = ctx
+        self.logits = None                    # [rows, vocab] float32 of the last step (a fixed buffer once captured)
+        self.filled = None                    # what fill() last wrote: [(slot, pages held)] per row
+        self.lengths = None                   # tokens each of those sequences has cached, as the device positions stand
+        self.tok_copied = torch.cuda.Event()
         self.temps = d["temps"].view(torch.float32)
         self.seeds = d["seeds"]
         self.sampler = Sampler(runner.vocab_size, rows, dev)
@@ -166,10 +172,20 @@ class DecodeState:
                 pages = cache.page_rows(g, [s["slot"]])[0][:self.width]
                 t[r, :len(pages)] = pages
         self.dev.copy_(self.host, non_blocking=True)
+        self.filled = [(s["slot"], cache.pages_held(s["slot"])) for s in seqs]
+        self.lengths = [s["pos"] for s in seqs]
+
+    def set_tokens(self, tokens):
+        """Overwrites the token ids of the first len(tokens) rows (a replay that forces its tokens)."""
+        n = len(tokens)
+        self.tok_copied.synchronize()         # the pinned buffer is free again
+        self.h["tok"][:n] = tokens
+        self.dev[:n].copy_(self.host[:n], non_blocking=True)     # the token ids are the first array of the buffer
+        self.tok_copied.record()
 
     def body(self, advance=True, out_tok=None):
-        logits = self.runner.model.forward(self.ctx, self.runner.cache)
-        self.sampler(logits, self.temps, self.seeds, self.ctx.row_pos, None,
+        self.logits = self.runner.model.forward(self.ctx, self.runner.cache)
+        self.sampler(self.logits, self.temps, self.seeds, self.ctx.row_pos, None,
                      self.ctx.tok if out_tok is None else out_tok, advance)
 
     def capture(self):
@@ -203,18 +219,20 @@ class DecodeState:
         return _Pending(self.ring[k], self.events[k], n)
 
 
-class GpuBackend:
-    """``run_batch``'s backend on the real model. One instance serves many batches one after
-    another; decode states (and their graphs) are kept per (rows, table width)."""
+class DecodeLoop:
+    """One-token steps of a runner's sequences through decode states: token ids, positions and page
+    tables at fixed addresses, the step replayed as a CUDA graph (or launched plainly). The states,
+    and their graphs, are kept per (rows, table width). Generation decodes through it, and a replay
+    of given tokens can (``forced_step``), so the logits of this path can be looked at too."""
 
-    def __init__(self, runner, use_graph=True, max_prefill_tokens=32768):
+    def __init__(self, runner, use_graph=True):
         self.runner, self.use_graph = runner, use_graph
-        self.max_prefill_tokens = max_prefill_tokens   # most prompt tokens one step runs (bounds the activations)
         self.states = {}
         self.prepared = 0
-        self.seqs = None
+        self.state = None
 
-    def _state(self, n_live, max_len):
+    def state_for(self, n_live, max_len):
+        """The decode state for ``n_live`` sequences that will grow to at most ``max_len`` tokens."""
         rows = bucket_rows(n_live)
         width = bucket_rows((max_len + PAGE - 1) // PAGE)
         if max_len > self.prepared:           # position tables grow: graphs captured before are stale
@@ -224,7 +242,60 @@ class GpuBackend:
         st = self.states.get((rows, width))
         if st is None:
             st = self.states[(rows, width)] = DecodeState(self.runner, rows, width)
+        self.state = st
         return st
+
+    def run(self):
+        """Launches one step of the current state; its slots' cached lengths move on by one."""
+        st = self.state
+        if self.use_graph and st.graph is None:
+            st.capture()
+        st.run()
+        cache = self.runner.cache
+        for slot, _ in st.filled:
+            cache.commit(slot, 1)
+        st.lengths = [n + 1 for n in st.lengths]
+
+    @torch.inference_mode()
+    def forced_step(self, entries):
+        """One token per sequence, given: entries [(slot, [token], want)]. Returns float32 logits of
+        the entries whose ``want`` is not empty, in order. The state is filled anew when the
+        sequences or their pages are not the ones it holds; otherwise only the tokens are written
+        and the positions are those the last step left on the device."""
+        cache = self.runner.cache
+        for slot, tokens, _ in entries:
+            if len(tokens) != 1:
+                raise ValueError("a decode step takes exactly one token per sequence")
+            cache.reserve(slot, 1)
+        now = [(slot, cache.pages_held(slot)) for slot, _, _ in entries]
+        st = self.state
+        max_len = max(cache.length[slot] for slot, _, _ in entries) + 1
+        if st is None or st.filled != now or st.lengths != [cache.length[slot] for slot, _, _ in entries] \
+                or st.width * PAGE < max_len or max_len > self.prepared:
+            st = self.state_for(len(entries), max_len)
+            st.fill([dict(slot=slot, token=tokens[0], pos=cache.length[slot], temperature=0.0, seed=0)
+                     for slot, tokens, _ in entries])
+        else:
+            st.set_tokens([tokens[0] for _, tokens, _ in entries])
+        self.run()
+        rows = [i for i, (_, _, want) in enumerate(entries) if want]
+        return st.logits[rows] if rows else st.logits[:0]
+
+
+class GpuBackend:
+    """``run_batch``'s backend on the real model. One instance serves many batches one after
+    another. Prompts go through the step function (``Runner.step``), decoding through the
+    runner's ``DecodeLoop``."""
+
+    def __init__(self, runner, use_graph=True, max_prefill_tokens=32768):
+        self.runner = runner
+        self.loop = DecodeLoop(runner, use_graph)
+        self.max_prefill_tokens = max_prefill_tokens   # most prompt tokens one step runs (bounds the activations)
+        self.seqs = None
+
+    @property
+    def state(self):
+        return self.loop.state
 
     def _prefill_plan(self, lengths):
         """Steps of the prefill: each a list of (sequence, first token, end token). Whole sequences
@@ -255,38 +326,31 @@ class GpuBackend:
         try:
             for p in prompts:
                 slots.append(r.begin())
-                r.cache.reserve(slots[-1], len(p) + params.max_new_tokens)
-        except Exception:
+                r.cache.reserve(slots[-1], len(p) + params.max_new_tokens)   # every page the sequence will need: the
+        except Exception:                                                    # decode state's page tables stay as they are
             for s in slots:
                 r.end(s)
             raise
         self.seqs = [dict(slot=s, token=0, pos=len(p), temperature=params.temperature, seed=sd, prompt_len=len(p))
                      for s, p, sd in zip(slots, prompts, seeds)]
         self.max_len = max(len(p) for p in prompts) + params.max_new_tokens
-        st = self.state = self._state(len(prompts), self.max_len)
+        st = self.loop.state_for(len(prompts), self.max_len)
         st.fill(self.seqs)
         for step in self._prefill_plan([len(p) for p in prompts]):
             # logits only where a prompt ends; the first token of those sequences is sampled at once
             ended = [i for i, _, p1 in step if p1 == len(prompts[i])]
-            ctx = r.context([(slots[i], prompts[i][p0:p1], [p1 - p0 - 1] if p1 == len(prompts[i]) else [])
-                             for i, p0, p1 in step])
-            logits = r.model.forward(ctx, r.cache)
-            for i, p0, p1 in step:
-                r.cache.commit(slots[i], p1 - p0)
+            logits, ctx = r.step([(slots[i], prompts[i][p0:p1], [p1 - p0 - 1] if p1 == len(prompts[i]) else [])
+                                  for i, p0, p1 in step], with_context=True)
             if ended:
                 lo, hi = ended[0], ended[-1] + 1          # sequences are taken in order: a contiguous range
                 st.sampler(logits, st.temps[lo:hi], st.seeds[lo:hi], ctx.row_pos, ctx.want_rows, st.ctx.tok[lo:hi], False)
-        api.gemm_tc_check()
         self.live = list(range(len(prompts)))
         return st.read(len(prompts))
 
     @torch.inference_mode()
     def decode(self):
-        st = self.state
-        if self.use_graph and st.graph is None:
-            st.capture()
-        st.run()
-        return st.read(len(self.live))
+        self.loop.run()
+        return self.loop.state.read(len(self.live))
 
     @torch.inference_mode()
     def repack(self, rows):
@@ -301,8 +365,7 @@ class GpuBackend:
             self.runner.end(self.seqs[i]["slot"])
             self.seqs[i]["slot"] = None
         self.live = [r[0] for r in rows]
-        self.state = self._state(len(rows), self.max_len)
-        self.state.fill(seqs)
+        self.loop.state_for(len(rows), self.max_len).fill(seqs)
 
     def finish(self):
         if self.seqs is None:

@@ -6,6 +6,7 @@ import torch
 
 from ..csrc import api
 from ..parts import ParamDecl, Runtime, build_part
+from ..parts.block import add_norm
 from ..parts.linear import STORE_F32, linear
 from ..parts.norm import RMSNorm
 
@@ -35,10 +36,8 @@ class CausalLM:
         self._entry_requests = [self.blocks[owners[c]].cache_requests() for c in range(n_entries)]
         self.embed = self.head = None
         self.tied = None
-        # decode products ask the matrix used next into L2 while they run; measured 8 to 30 % slower
-        # on B200 whatever the amount (the hints delay the demand loads), so off
-        self.prefetch = False
-        self._prefetcher = None
+        # index arrays the parts' kernels want built for every step (engine.batch.build_context), once per key
+        self.step_plans = list({p.key: p for b in self.blocks for p in b.step_plans()}.values())
 
     # -- parameters --------------------------------------------------------------------------
     def param_decls(self, tied):
@@ -73,45 +72,33 @@ class CausalLM:
             b.prepare(max_positions)
 
     def weight_bytes_per_step(self):
-        """Bytes of weights a decode step reads: every matrix once, the embedding only when it is
-        also the head."""
+        """Bytes of weights a decode step reads: what every part says it streams once a step, for
+        every run of a layer in the schedule, and the head (the embedding is read by row only, so it
+        counts only where it is also the head)."""
         total = self.head.numel() * self.head.element_size()
-        for b in self.blocks:
-            for t in (b.mixer.__dict__, b.feed_forward.__dict__):
-                total += sum(v.numel() * v.element_size() for v in t.values() if isinstance(v, torch.Tensor))
+        for e in self.spec.schedule:
+            total += sum(w.numel() * w.element_size() for w in self.blocks[e.layer].step_weights())
         return total
 
-    def weights_in_order(self):
-        """The matrices one step streams, in the order of use (for the decode-step prefetcher)."""
-        out = []
-        for e in self.spec.schedule:
-            out += self.blocks[e.layer].weights_in_order()
-        return out + [self.head]
-
     # -- one step ----------------------------------------------------------------------------
-    def forward(self, ctx, cache):
+    def forward(self, ctx, cache, tap=None):
+        """``tap(k, h)``: called after the k-th schedule entry with the residual stream as it then
+        stands (that entry's feed-forward output added in): for dumps that look for the layer where
+        two runs part ways. It costs a launch and a copy per entry, so it is for debugging only."""
         s, rt = self.spec, self.rt
-        ctx.prefetcher = None
-        if self.prefetch and ctx.is_decode and rt.dtype == torch.bfloat16 and ctx.n_tok <= api.STREAM_BEST_ROWS:
-            if self._prefetcher is None:
-                from .prefetch import WeightPrefetcher
-                self._prefetcher = WeightPrefetcher(self.weights_in_order())
-            ctx.prefetcher = self._prefetcher
         h = torch.empty((ctx.n_tok, s.hidden_size), dtype=torch.float32, device=rt.device)
         a = torch.empty((ctx.n_tok, s.hidden_size), dtype=rt.dtype, device=rt.device)
         first = self.blocks[s.schedule[0].layer]
-        fused = getattr(first.norm_in, "weight", None) is not None and hasattr(first.norm_in.spec, "eps")
+        fused = isinstance(first.norm_in, RMSNorm)       # the embedding kernel computes RMSNorm and nothing else
         api.embed_rmsnorm(ctx.tok, self.embed, first.norm_in.weight if fused else None,
                           first.norm_in.spec.eps if fused else 0.0, h, a)
         pending = None
         for i, e in enumerate(s.schedule):
             pending = self.blocks[e.layer].forward(ctx, h, pending, cache.views(e.cache), e.writes,
                                                    a if (i == 0 and fused) else None)
+            if tap is not None:
+                tap(i, h + (pending.ws.sum(0) if isinstance(pending, api.Partial) else pending.to(torch.float32)))
         if ctx.n_want == 0:
             return torch.empty((0, s.vocab_size), dtype=torch.float32, device=rt.device)
-        an = torch.empty((ctx.n_want, s.hidden_size), dtype=rt.dtype, device=rt.device)
-        if isinstance(pending, api.Added) and not isinstance(self.final_norm, RMSNorm):
-            pending = None                      # already in h; only RMSNorm knows the marker
-        self.final_norm.add_forward(h, pending, an, rows=ctx.want_rows)
+        an = add_norm(self.final_norm, h, pending, rt.dtype, rows=ctx.want_rows)
         return linear(an, self.head, STORE_F32)
-

@@ -41,16 +41,18 @@ class Runner:
                 raise ValueError(f"token id outside [0, {self.vocab_size})")
         if len({e[0] for e in entries}) != len(entries):
             raise ValueError("a slot appears twice in one step")
-        return build_context(self.cache, entries, self.device, self._scratch, pad_to)
+        return build_context(self.cache, entries, self.device, self._scratch, pad_to, self.model.step_plans)
 
     @torch.inference_mode()
-    def step(self, entries):
+    def step(self, entries, tap=None, with_context=False):
         """entries: list of (slot, tokens, want). Returns float32 logits [sum(len(want)), vocab]
-        on the device, in the order of the entries and of each ``want``."""
+        on the device, in the order of the entries and of each ``want``. ``tap``: see
+        ``CausalLM.forward``. ``with_context``: also return the step's ``StepContext`` (the
+        generation loop samples from the logits with its positions and wanted rows)."""
         ctx = self.context(entries)
-        logits = self.model.forward(ctx, self.cache)
+        logits = self.model.forward(ctx, self.cache, tap)
         for slot, tokens, _ in entries:
             self.cache.commit(slot, len(tokens))
         if not ctx.is_decode:
             api.gemm_tc_check()
-        return logits
+        return (logits, ctx) if with_context else logits

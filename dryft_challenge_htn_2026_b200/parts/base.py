@@ -8,18 +8,27 @@ in: sizes and constants come from the specification only.
 
 Interfaces (duck-typed; see the classes in this package for the working examples):
 
-* norm:            ``forward(x, out)``, ``add_forward(h, delta, out, rows=None)`` with ``h`` the
-                   float32 residual stream, updated in place by ``delta``.
-* position:        ``tables(n)`` / ``apply(...)`` used by the mixer that owns it.
+* norm:            ``add_forward(h, delta, out, rows=None)`` with ``h`` the float32 residual
+                   stream, updated in place by ``delta`` (None: nothing to add) unless ``rows``
+                   selects rows, which are then normalised into ``out`` without touching ``h``.
+                   ``takes_partial = True`` if ``delta`` may be a ``csrc.api.Partial``.
+* position:        ``fused_tables = True`` and ``tables(n)``, or ``apply(qkv, ctx, nh, nkv, hd)``;
+                   used by the mixer that owns it.
 * mixer:           ``cache_requests()`` -> list of ``cache.KVRequest`` / ``cache.StateRequest``;
                    ``forward(ctx, views, a, writes)`` -> [tokens, hidden] in the compute dtype.
                    ``views`` are the cache views answering the requests, ``ctx`` the step's
                    ``engine.StepContext`` (token rows, their sequences and positions, page tables).
 * feed-forward:    ``forward(ctx, a)`` -> [tokens, hidden].
+
+Every part may also give ``step_weights()`` (the tensors a step reads once whatever the batch: the
+bytes a decode step must stream), ``step_plans()`` (``StepPlan`` objects: index arrays its kernels
+need each step, built on the host from the step's sequences and uploaded with the step context)
+and ``prepare(max_positions)``; the defaults are empty.
 """
 from dataclasses import dataclass
 from typing import Tuple
 
+import numpy as np
 import torch
 
 
@@ -37,6 +46,17 @@ class ParamDecl:
     keep_float32: bool = False  # small vectors (norm weights) are held in float32 for every dtype
 
 
+class StepPlan:
+    """Index data a part's kernels want for every step, e.g. a list of work tiles. ``key`` names
+    it (equal keys are built once a step, whoever asks); ``build(seqs)`` gets the step's sequences
+    as numpy arrays ``lens`` (new tokens each), ``pos0`` (tokens cached before) and ``is_decode``,
+    and returns an int32 array, which reaches the kernels as ``ctx.plans[key]`` on the device."""
+    key = None
+
+    def build(self, lens, pos0, is_decode):
+        return np.zeros((0,), np.int32)
+
+
 class Part:
     def __init__(self, spec, rt):
         self.spec = spec
@@ -47,6 +67,15 @@ class Part:
 
     def bind(self, tensors):
         """``tensors``: name (as declared) -> tensor on the device, already cast."""
+
+    def step_weights(self):
+        return []
+
+    def step_plans(self):
+        return []
+
+    def prepare(self, max_positions):
+        """Called before steps that reach positions up to ``max_positions`` (tables that grow)."""
 
 
 _PART_CLASSES = {}

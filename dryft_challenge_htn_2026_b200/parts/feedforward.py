@@ -7,8 +7,6 @@ from .linear import SILU, linear
 
 
 class GatedMLP(Part):
-    fuses_residual = False   # as GQAAttention.fuses_residual
-
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         if spec.activation != "silu":
@@ -28,12 +26,11 @@ class GatedMLP(Part):
         self.w_gate_up = torch.cat([tensors.pop("gate_proj.weight"), tensors.pop("up_proj.weight")], 0).contiguous()
         self.w_down = tensors.pop("down_proj.weight").contiguous()
 
-    def weights_in_order(self):
+    def step_weights(self):
         return [self.w_gate_up, self.w_down]
 
-    def forward(self, ctx, a, residual=None):
-        return linear(linear(a, self.w_gate_up, SILU, ctx), self.w_down, ctx=ctx, allow_partial=True,
-                      residual=residual)
+    def forward(self, ctx, a):
+        return linear(linear(a, self.w_gate_up, SILU), self.w_down, allow_partial=True)
 
 
 register_part(GatedMLPSpec, GatedMLP)

@@ -55,10 +55,15 @@ def list_tensors(folder):
 def load_weights(model, folder):
     """Checks the folder against ``model`` and binds the tensors. Ties the head to the embedding
     when the spec says so, or, when the spec leaves it open, when the files have no head tensor
-    (as the reference decides it, engine/engine.py:290)."""
+    (as the reference decides it, engine/engine.py:290). A head tensor in the files of a model whose
+    config ties the head is accepted (published checkpoints of tied models ship one): its shape is
+    checked, and it is bound as the head, as the reference does with a head tensor it finds."""
     have = list_tensors(folder)
     spec = model.spec
-    tied = spec.tie_embeddings if spec.tie_embeddings is not None else spec.head_name not in have
+    if spec.tie_embeddings and spec.head_name in have:
+        tied = False
+    else:
+        tied = spec.tie_embeddings if spec.tie_embeddings is not None else spec.head_name not in have
     decls = model.param_decls(tied)
     missing = [n for n in decls if n not in have]
     unexpected = [n for n in have if n not in decls]

@@ -122,18 +122,24 @@ def test_random_sequence_lifecycles_keep_the_books_straight():
 def test_build_context_rows_positions_and_tiles():
     cache = Cache([[KV]], max_tokens=64 * 16, max_slots=8, device="cpu")
     a, b, c = cache.begin(), cache.begin(), cache.begin()
-    ctx = build_context(cache, [(a, [1] * 5, [4]), (b, [2] * 130, [0, 129]), (c, [3], [0])], torch.device("cpu"))
+    from dryft_challenge_htn_2026_b200.parts.attention import QueryTiles
+    narrow, wide = QueryTiles(64), QueryTiles(128)
+    ctx = build_context(cache, [(a, [1] * 5, [4]), (b, [2] * 130, [0, 129]), (c, [3], [0])], torch.device("cpu"),
+                        plans=[narrow, wide, QueryTiles(64)])       # parts' planning data: built once per key
     assert (ctx.n_tok, ctx.n_seq, ctx.n_want, ctx.is_decode) == (136, 3, 4, False)
     assert ctx.cu_q.tolist() == [0, 5, 135, 136] and ctx.want_rows.tolist() == [4, 5, 134, 135]
     assert ctx.row_pos[:5].tolist() == [0, 1, 2, 3, 4] and ctx.row_pos[5:135].tolist() == list(range(130))
     assert ctx.row_seq[4:6].tolist() == [0, 1] and ctx.seq_pos0.tolist() == [0, 0, 0]
-    assert sorted(map(tuple, ctx.tiles.tolist())) == [(0, 0), (1, 0), (1, 64), (1, 128), (2, 0)]
-    assert tuple(ctx.tiles[0].tolist()) == (1, 128)              # the tile that sees most keys goes first
-    assert sorted(map(tuple, ctx.tiles_wide.tolist())) == [(0, 0), (1, 0), (1, 128), (2, 0)]
+    assert set(ctx.plans) == {narrow.key, wide.key}
+    tiles = ctx.plans[narrow.key]
+    assert sorted(map(tuple, tiles.tolist())) == [(0, 0), (1, 0), (1, 64), (1, 128), (2, 0)]
+    assert tuple(tiles[0].tolist()) == (1, 128)                  # the tile that sees most keys goes first
+    assert sorted(map(tuple, ctx.plans[wide.key].tolist())) == [(0, 0), (1, 0), (1, 128), (2, 0)]
     assert ctx.tables[0].shape == (3, 3) and ctx.tables[0][0].tolist()[1:] == [-1, -1]
     for s, n in ((a, 5), (b, 130), (c, 1)):
         cache.commit(s, n)
-    ctx = build_context(cache, [(b, [7], [0]), (a, [8], [0])], torch.device("cpu"), pad_to=4)
+    ctx = build_context(cache, [(b, [7], [0]), (a, [8], [0])], torch.device("cpu"), pad_to=4, plans=[narrow])
+    assert ctx.plans[narrow.key].numel() == 0                    # a decode step has no query tiles
     assert ctx.is_decode and ctx.n_tok == 4 and ctx.n_seq == 4 and ctx.n_want == 2
     assert ctx.row_pos.tolist() == [130, 5, -1, -1] and ctx.tables[0].shape[0] == 4
     assert ctx.max_position == 130

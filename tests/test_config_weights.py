@@ -109,18 +109,32 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     del t["model.norm.weight"]
     t["model.layers.0.mlp.gate_proj.weight"] = torch.zeros(128, 60)
     t["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(64)
-    t["lm_head.weight"] = torch.zeros(256, 64)                        # tied model: not expected
+    t["lm_head.weight"] = torch.zeros(256, 60)                        # a head in a tied model is accepted; its shape is checked
     save_file(t, path)
     m = CausalLM(dk.config_from_folder(folder).to_spec(), torch.float32, "cpu")
     with pytest.raises(dk.WeightError) as e:
         dk.load_weights(m, folder)
     err = e.value
     assert err.missing == ["model.layers.1.self_attn.k_norm.weight", "model.norm.weight"]
-    assert err.unexpected == ["lm_head.weight", "model.layers.0.self_attn.q_proj.bias"]
-    assert [w[0] for w in err.wrong_shape] == ["model.layers.0.mlp.gate_proj.weight"]
+    assert err.unexpected == ["model.layers.0.self_attn.q_proj.bias"]
+    assert [w[0] for w in err.wrong_shape] == ["lm_head.weight", "model.layers.0.mlp.gate_proj.weight"]
     text = str(err)
-    for needle in ("missing (2)", "unexpected (2)", "wrong shape (1)", "[128, 60]", "[128, 64]"):
+    for needle in ("missing (2)", "unexpected (1)", "wrong shape (2)", "[128, 60]", "[128, 64]"):
         assert needle in text
+
+
+def test_a_tied_checkpoint_that_ships_a_head_tensor_loads(tmp_path):
+    """Published checkpoints of models whose config ties the head still hold lm_head.weight; the
+    reference binds a head tensor whenever the files have one (engine/engine.py:290)."""
+    folder = make_folder(tmp_path, "A")
+    path = os.path.join(folder, "model.safetensors")
+    t = load_file(path)
+    t["lm_head.weight"] = t["model.embed_tokens.weight"].clone()
+    save_file(t, path)
+    m = CausalLM(dk.config_from_folder(folder).to_spec(), torch.float32, "cpu")
+    assert m.spec.tie_embeddings is True
+    dk.load_weights(m, folder)
+    assert torch.equal(m.head, m.embed)
 
 
 def test_schedule_is_checked():

@@ -160,6 +160,17 @@ def test_qk_norm_rope_write(dtype, nh, nkv, hd):
                            s["v_store"], nh, nkv, hd, 1e-6, write_kv=False)
     assert torch.equal(q_out.view(T, nh, hd)[keep], qkv.view(T, nh + 2 * nkv, hd)[:, :nh][keep])
     assert torch.equal(s["k_store"], k_before)
+    # the norm alone into a dense tensor (the step before a position encoding that a part applies itself):
+    # q and k normalised, v copied, the cache and q_out left alone
+    dense = torch.zeros_like(qkv)
+    q_before = q_out.clone()
+    api.qk_norm_rope_write(qkv, None, qn, kn, None, None, s["row_pos"], s["row_seq"], s["table"], s["k_store"],
+                           s["v_store"], nh, nkv, hd, 1e-6, dense_out=dense)
+    d = dense.view(T, nh + 2 * nkv, hd)
+    close(d[:, :nh][keep], rms(x[:, :nh], qn, 1e-6)[keep], dtype, "dense q")
+    close(d[:, nh:nh + nkv][keep], rms(x[:, nh:nh + nkv], kn, 1e-6)[keep], dtype, "dense k")
+    assert torch.equal(d[:, nh + nkv:][keep], qkv.view(T, nh + 2 * nkv, hd)[:, nh + nkv:][keep])
+    assert torch.equal(s["k_store"], k_before) and torch.equal(q_out, q_before) and float(dense[4].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -255,34 +266,6 @@ def test_sgemm(M, N, K):
     assert torch.equal(one[0], out[M // 2])
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
-@pytest.mark.parametrize("N,K", [(64, 64), (300, 72), (200, 2560), (2560, 9728 // 4 + 8)])
-def test_gemv_bf16(M, N, K):
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=21), rnd(N, K, dtype=torch.bfloat16, seed=22, scale=0.05)
-    ref = x.float() @ w.float().T
-    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    api.gemv_bf16(x, w, out)
-    close(out, ref, torch.bfloat16, "gemv store")
-    out32 = torch.empty(M, N, device=DEV)
-    api.gemv_bf16(x, w, out32, api.MODE_STORE_F32)
-    assert float((out32 - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))   # float32 accumulate and store
-    # plans (slices of K per tile, warps per block, most blocks): split K gives partial sums, few
-    # blocks make the warps loop over units
-    for plan in [(1, 8, 296), (1, 3, 2), (2, 8, 296), (4, 1, 5), (16, 8, 1000)]:
-        r = api.gemv_bf16(x, w, None, api.MODE_STORE_F32, plan=plan)
-        if plan[0] > 1:
-            assert isinstance(r, api.Partial) and tuple(r.ws.shape) == (plan[0], M, N)
-            r = r.ws.sum(0)
-        assert float((r - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
-    close(api.gemv_bf16(x, w, None, api.MODE_STORE, plan=(4, 8, 296)).sum(), ref, torch.bfloat16, "summed partials")
-    if N % 2 == 0:
-        half = N // 2
-        o = torch.empty(M, half, dtype=torch.bfloat16, device=DEV)
-        api.gemv_bf16(x, w, o, api.MODE_SILU)
-        g, u = ref[:, :half], ref[:, half:]
-        close(o, g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gemv silu")
-
-
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_consumers_add_up_partial_sums(dtype):
     """add_rmsnorm and qk_norm_rope_write given split-K partial sums equal the same kernels given the sum."""
@@ -315,13 +298,16 @@ def test_consumers_add_up_partial_sums(dtype):
         close(a, b, dtype, "qk_norm_rope_write(partial)")
 
 
-def test_gemv_refuses_what_it_cannot_do():
-    x, w = rnd(65, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
+def test_kernels_refuse_what_they_cannot_do():
+    x, w = rnd(17, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
     with pytest.raises(api.KernelError):
-        api.gemv_bf16(x, w, torch.empty(65, 32, dtype=torch.bfloat16, device=DEV))
+        api.gemv_stream(x, w)                                   # more than 16 rows
+    x, w = rnd(2, 24, dtype=torch.bfloat16), rnd(32, 24, dtype=torch.bfloat16)
+    with pytest.raises(api.KernelError):
+        api.gemv_stream(x, w)                                   # K no multiple of 16
     x, w = rnd(2, 12, dtype=torch.bfloat16), rnd(32, 12, dtype=torch.bfloat16)
     with pytest.raises(api.KernelError):
-        api.gemv_bf16(x, w, torch.empty(2, 32, dtype=torch.bfloat16, device=DEV))
+        api.gemm_tc(x, w)                                       # K no multiple of 8
     with pytest.raises(api.KernelError):
         api.attention_prefill_bf16(rnd(1, 24, dtype=torch.bfloat16), rnd(1, 24, dtype=torch.bfloat16), None, None,
                                    torch.zeros(1, 2, dtype=torch.int32, device=DEV),
@@ -370,74 +356,42 @@ def test_sampler_greedy_and_gumbel(V):
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("N,K", [(64, 64), (300, 96), (200, 2560), (2560, 2448), (100, 4096)])
+@pytest.mark.parametrize("N,K", [(64, 64), (300, 96), (200, 2560), (2560, 2448), (100, 4096), (136, 5120), (40, 5552), (48, 9728)])
 def test_gemv_stream(M, N, K):
-    """The streaming product against x.w^T: every mode, slices of K, few and many blocks."""
+    """The streaming product against x.w^T: every mode, slices of K, few and many blocks, both block
+    shapes (four streaming warps, eight for the longer rows of x)."""
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=51), rnd(N, K, dtype=torch.bfloat16, seed=52, scale=0.05)
     ref = x.float() @ w.float().T
-    if K <= 2560:
-        close(api.gemv_stream(x, w, None, api.MODE_STORE, (1, 296)), ref, torch.bfloat16, "stream store")
-    for plan in [(1, 1), (1, 5), (2, 296), (4, 7), (8, 296)]:
-        if (-(-K // plan[0]) + 15) // 16 * 16 > 2560:
+    fits = lambda sk, warps: api._stream_smem(M, K, sk, warps) <= 227 * 1024
+    for sk, blocks, warps in [(1, 296, 4), (1, 1, 4), (1, 5, 8), (1, 148, 8), (2, 296, 4), (4, 7, 8), (8, 296, 4)]:
+        plan = (sk, blocks, warps)
+        if not fits(sk, warps):
             with pytest.raises(api.KernelError):
                 api.gemv_stream(x, w, None, api.MODE_STORE_F32, plan)
             continue
         r = api.gemv_stream(x, w, None, api.MODE_STORE_F32, plan)
-        if plan[0] > 1:
-            assert isinstance(r, api.Partial) and tuple(r.ws.shape) == (plan[0], M, N)
+        if sk > 1:
+            assert isinstance(r, api.Partial) and tuple(r.ws.shape) == (sk, M, N)
             r = r.ws.sum(0)
         assert float((r - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max())), plan
-    if N % 2 == 0 and K <= 2560:
-        half = N // 2
-        g, u = ref[:, :half], ref[:, half:]
-        close(api.gemv_stream(x, w, None, api.MODE_SILU, (1, 296)), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "stream silu")
+        if sk == 1:
+            close(api.gemv_stream(x, w, None, api.MODE_STORE, plan), ref, torch.bfloat16, f"stream store {plan}")
+            if N % 2 == 0:
+                half = N // 2
+                g, u = ref[:, :half], ref[:, half:]
+                close(api.gemv_stream(x, w, None, api.MODE_SILU, plan), g / (1 + torch.exp(-g)) * u, torch.bfloat16,
+                      f"stream silu {plan}")
     # the plan the model uses
     plan = api.stream_plan(M, N, K, api.MODE_STORE, allow_partial=True)
     r = api.gemv_stream(x, w, None, api.MODE_STORE, plan)
     close(r.sum() if isinstance(r, api.Partial) else r, ref, torch.bfloat16, "stream planned")
-    assert api.stream_plan(M, N, 9728, api.MODE_SILU) is None and api.stream_plan(M, N, 9728, api.MODE_STORE, True)[0] >= 4
-
-
-@pytest.mark.parametrize("nh,nkv,hd,window,nsplit", [(4, 2, 16, 0, 1), (32, 8, 128, 0, 6), (6, 2, 48, 0, 8),
-                                                     (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 16)])
-@pytest.mark.parametrize("as_partial", [False, True])
-def test_attention_decode_fused(nh, nkv, hd, window, nsplit, as_partial):
-    """Decode attention that norms and rotates the new token's q and k itself and writes the cache,
-    against the separate kernels: same outputs, and the cache holds the same new keys and values."""
-    before = [0, 63, 64, 300, 1000, 5]
-    n = len(before)
-    s = paged_setup(before, [1] * n, nkv, hd, torch.bfloat16, seed=60)
-    width = (nh + 2 * nkv) * hd
-    parts = rnd(3, n + 1, width, seed=61, scale=0.6)
-    qkv = parts.sum(0).to(torch.bfloat16)
-    arg = api.Partial(parts) if as_partial else qkv
-    qn, kn = 1 + 0.1 * rnd(hd, seed=62), 1 + 0.1 * rnd(hd, seed=63)
-    cos, sin = plain.rope_tables(1e4, hd, 1100)
-    cos_h, sin_h = cos[:, :hd // 2].contiguous().to(DEV), sin[:, :hd // 2].contiguous().to(DEV)
-    row_pos = torch.cat([s["row_pos"], torch.tensor([-1], dtype=torch.int32, device=DEV)])     # one padding row
-    table = torch.cat([s["table"], -torch.ones(1, s["table"].shape[1], dtype=torch.int32, device=DEV)])
-    row_seq = torch.arange(n + 1, dtype=torch.int32, device=DEV)
-    # reference: the separate kernels on a copy of the cache
-    k_ref, v_ref = s["k_store"].clone(), s["v_store"].clone()
-    q = torch.empty(n + 1, nh * hd, dtype=torch.bfloat16, device=DEV)
-    api.qk_norm_rope_write(qkv if not as_partial else api.Partial(parts), q, qn, kn, cos_h, sin_h, row_pos, row_seq, table,
-                           k_ref, v_ref, nh, nkv, hd, 1e-6)
-    want = torch.empty_like(q)
-    api.attention_generic(q, want, k_ref, v_ref, row_pos, row_seq, table, nh, nkv, hd, window, hd ** -0.5)
-    out = torch.full_like(q, float("nan"))
-    ws = api.attention_decode_ws(n + 1, nh, hd, nsplit, DEV)
-    for _ in range(2):                                               # twice: the second run finds its own writes
-        api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh,
-                                   nkv, hd, window, hd ** -0.5, nsplit, *ws)
-        close(out[:n], want[:n], torch.bfloat16, "fused decode attention")
-        assert float(out[n:].float().abs().max()) == 0.0
-    assert torch.equal(s["k_store"], k_ref) and torch.equal(s["v_store"], v_ref)
-    # a layer that only reads another layer's cache: nothing is written
-    k0 = s["k_store"].clone()
-    api.attention_decode_fused(arg, out, qn, kn, cos_h, sin_h, 1e-6, s["k_store"], s["v_store"], row_pos, table, nh, nkv, hd,
-                               window, hd ** -0.5, nsplit, *ws, write_kv=False)
-    assert torch.equal(s["k_store"], k0)
-    close(out[:n], want[:n], torch.bfloat16, "fused decode attention, read-only")
+    # the rows of x of one slice must fit a block: beyond that the gated product has no plan, the plain one is cut
+    assert api.stream_plan(M, N, 20000, api.MODE_SILU) is None and api.stream_plan(M, N, 20000, api.MODE_STORE, True)[0] >= 2
+    if M <= 8:
+        assert api.stream_plan(M, N, 5120, api.MODE_SILU) == (1, api.sm_count(), 8)
+        assert api.stream_plan(M, N, 9728, api.MODE_SILU) == (1, api.sm_count(), 4)   # 8 rows of 9,728: one block of four warps
+    else:
+        assert api.stream_plan(M, N, 9728, api.MODE_SILU) is None
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (100, 300, 72), (300, 200, 136), (1000, 520, 2560), (65, 2560, 1024)])
@@ -510,13 +464,11 @@ def test_gemm_tc_qkv_epilogue(nh, nkv, hd, K, before, new, norm, rope):
     (2, 1, 128, 0, [0], [128]), (8, 2, 128, 0, [0, 100, 0, 64, 130], [70, 150, 1, 64, 5]), (4, 4, 64, 0, [0, 100], [200, 129]),
     (3, 1, 64, 90, [0, 100], [200, 129]), (6, 2, 128, 40, [300, 0], [140, 400]),
     (16, 4, 64, 0, [0, 100, 37, 64, 300], [700, 450, 300, 129, 1000]), (16, 2, 128, 200, [50, 0, 500], [900, 640, 1100])])
-@pytest.mark.parametrize("step_keys", [64, 128])
-def test_attention_prefill_tc(nh, nkv, hd, window, before, new, step_keys, monkeypatch):
+def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
     """The tcgen05 prefill attention against the float32 reference: ragged chunks on top of cached
     tokens, several key blocks per tile (rescaling of O), group sizes 1..8, a window, padding rows;
     the last two cases have more (tile, head) items than the grid has blocks, so that a block works
     through several, with odd and even numbers of steps, on the same barriers."""
-    monkeypatch.setattr(api, "TC_ATTENTION_STEP_KEYS", step_keys)    # both builds: steps of one page (the default) and of two
     s = paged_setup(before, new, nkv, hd, torch.bfloat16, seed=90)
     q = rnd(s["n_tok"], nh * hd, dtype=torch.bfloat16, seed=91)
     tiles = sorted(((before[i] + min(q0 + 128, new[i]), i, q0) for i in range(len(new)) for q0 in range(0, new[i], 128)),
@@ -532,48 +484,6 @@ def test_attention_prefill_tc(nh, nkv, hd, window, before, new, step_keys, monke
                              hd ** -0.5)
     assert torch.equal(again, out)                                   # which block took which item changes nothing
     assert all(int(c.abs().sum()) == 0 for c in api._attn_sched.values())   # the work counter is left at zero
-
-
-@pytest.mark.parametrize("M,N,K", [(1, 2560, 4096), (8, 2560, 9728), (5, 72, 304), (16, 1000, 2560), (11, 264, 5008)])
-def test_gemv_stream_adds_into_the_residual_stream(M, N, K):
-    """Product added into float32 h in place, slices meeting inside the kernel; the sums of
-    squares it leaves are those of the new h; twice, so the counters must have come back to zero."""
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=70), rnd(N, K, dtype=torch.bfloat16, seed=71, scale=K ** -0.5)
-    h0 = rnd(M, N, seed=72)
-    want = h0 + x.float() @ w.float().t()
-    for sk in (1, 2, 4, 8):
-        if ((K + sk - 1) // sk + 15) // 16 * 16 > 2560 or K // sk < 16:
-            continue
-        for _ in range(2):
-            h = h0.clone()
-            r = api.gemv_stream(x, w, None, api.MODE_STORE, (sk, 296), residual=h)
-            assert isinstance(r, api.Added) and r.h is h
-            err = float((h - want).abs().max())
-            assert err <= 1e-4 * max(1.0, float(want.abs().max())), f"residual, {sk} slices: {err}"   # float32 sums, other order
-            sq_err = float((r.sq.sum(0)[:M] / (h * h).sum(1) - 1).abs().max())
-            assert sq_err <= 1e-5, f"sums of squares, {sk} slices: {sq_err}"
-
-
-@pytest.mark.parametrize("M,N,K", [(1, 6144, 2560), (8, 9728, 2560), (5, 72, 304), (16, 1000, 2000), (3, 96, 5008)])
-def test_gemv_stream_applies_a_deferred_norm(M, N, K):
-    h = rnd(M, K, seed=73, scale=3.0)
-    nw = 1 + 0.2 * rnd(K, seed=74)
-    eps = 1e-5
-    sq = torch.zeros((K + 15) // 16, 16, device=DEV)
-    pad = torch.zeros(M, sq.shape[0] * 16, device=DEV)
-    pad[:, :K] = h * h
-    sq[:, :M] = pad.view(M, -1, 16).sum(2).t()
-    x = (h * torch.rsqrt((h * h).mean(1, keepdim=True) + eps) * nw).to(torch.bfloat16)
-    lazy = api.Normed(h, sq, nw, eps, torch.bfloat16)
-    close(lazy.tensor(), x.float(), torch.bfloat16, "deferred norm, computed")
-    w = rnd(N, K, dtype=torch.bfloat16, seed=75, scale=K ** -0.5)
-    plan = api.stream_plan(M, N, K, api.MODE_STORE, True)
-    r = api.gemv_stream(lazy, w, None, api.MODE_STORE, plan)
-    r = r.sum() if isinstance(r, api.Partial) else r
-    close(r, x.float() @ w.float().t(), torch.bfloat16, "deferred norm, store")
-    if N % 2 == 0 and api.stream_plan(M, N // 2, K, api.MODE_SILU) is not None:
-        g, u = (x.float() @ w.float().t()).chunk(2, dim=1)
-        close(api.gemv_stream(lazy, w, None, api.MODE_SILU), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "deferred norm, silu")
 
 
 @pytest.mark.parametrize("M,N,K", [(64, 6144, 2560), (33, 2560, 4096), (128, 2560, 9728), (17, 300, 520), (100, 1000, 1288)])

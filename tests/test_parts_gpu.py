@@ -99,11 +99,11 @@ def test_attention_part_whole_then_token_by_token(dtype, H, nh, nkv, hd, window)
     cache = Cache([part.cache_requests()], 64 * 4, 4, DEV)
     slot = cache.begin()
     # 70 tokens in one step, then 20 one at a time: the part never knows the difference
-    ctx = build_context(cache, [(slot, [0] * 70, [])], DEV)
+    ctx = build_context(cache, [(slot, [0] * 70, [])], DEV, plans=part.step_plans())
     out = [tensor(part.forward(ctx, cache.views(0), a[:70].to(DEV)), dtype)]
     cache.commit(slot, 70)
     for p in range(70, S):
-        ctx = build_context(cache, [(slot, [0], [])], DEV)
+        ctx = build_context(cache, [(slot, [0], [])], DEV, plans=part.step_plans())
         out.append(tensor(part.forward(ctx, cache.views(0), a[p:p + 1].to(DEV)), dtype))
         cache.commit(slot, 1)
     close(torch.cat(out), ref, dtype, "attention part")
@@ -141,34 +141,7 @@ def test_block_part(dtype):
     ref, _ = plain.decoder_layer(h0, t, 0, dict(nh=nh, nkv=nkv, hd=hd, eps=1e-5, theta=1e5))
     cache = Cache([part.cache_requests()], 64 * 2, 2, DEV)
     slot = cache.begin()
-    ctx = build_context(cache, [(slot, [0] * 75, [])], DEV)
+    ctx = build_context(cache, [(slot, [0] * 75, [])], DEV, plans=part.step_plans())
     h = h0.to(DEV)
     pending = part.forward(ctx, h, None, cache.views(0))
     close(h + tensor(pending, dtype).float(), ref, dtype, "block")                   # the block leaves its last add to the next norm
-
-
-def test_attention_part_fused_decode_agrees_with_separate_kernels():
-    """The decode path whose attention kernel norms, rotates and writes the cache itself gives what the
-    path with the separate kernel gives."""
-    H, nh, nkv, hd = 64, 4, 2, 32
-    spec = AttentionSpec(H, nh, nkv, hd, hd ** -0.5, RMSNormSpec(hd, 1e-6), RotaryHalfSpec(hd, 1e4), None)
-    outs = []
-    for fused in (False, True):
-        part = build_part(spec, Runtime(DEV, torch.bfloat16))
-        part.fuse_decode = fused
-        bind(part, {k.split("self_attn.")[1]: v for k, v in mixer_weights(H, nh, nkv, hd, 70).items()}, torch.bfloat16)
-        cache = Cache([part.cache_requests()], 64 * 4, 4, DEV)
-        slots = [cache.begin(), cache.begin()]
-        a = rnd(80 + 3 + 10, H, seed=71).to(DEV, torch.bfloat16)
-        ctx = build_context(cache, [(slots[0], [0] * 80, []), (slots[1], [0] * 3, [])], DEV)
-        part.forward(ctx, cache.views(0), a[:83])
-        cache.commit(slots[0], 80), cache.commit(slots[1], 3)
-        steps = []
-        for i in range(5):
-            ctx = build_context(cache, [(slots[0], [0], []), (slots[1], [0], [])], DEV, pad_to=4)
-            x = torch.zeros(4, H, dtype=torch.bfloat16, device=DEV)
-            x[:2] = a[83 + 2 * i:85 + 2 * i]
-            steps.append(tensor(part.forward(ctx, cache.views(0), x), torch.bfloat16)[:2].float())
-            cache.commit(slots[0], 1), cache.commit(slots[1], 1)
-        outs.append(torch.cat(steps))
-    close(outs[1], outs[0].cpu(), torch.bfloat16, "fused vs separate decode")

@@ -7,16 +7,26 @@ from dryft_challenge_htn_2026_b200.csrc import api
 
 
 def test_stream_plan_keeps_a_slice_of_x_in_shared_memory_and_splits_only_when_allowed():
-    for M, N, K in itertools.product((1, 8, 16), (72, 2560, 6144, 151936), (304, 2560, 4096, 9728, 20000)):
+    sms = api.sm_count()
+    for M, N, K in itertools.product((1, 8, 16), (72, 2560, 6144, 151936), (304, 2560, 4096, 5120, 9728, 20000)):
         for mode, partial in ((api.MODE_STORE, False), (api.MODE_STORE, True), (api.MODE_STORE_F32, False), (api.MODE_SILU, False)):
             plan = api.stream_plan(M, N, K, mode, partial)
             if plan is None:                      # only when K needs slices that the caller or the epilogue cannot take
                 assert K > 2560 and (mode == api.MODE_SILU or not partial)
+                assert api._stream_smem(M, K, 1, 8) > 227 * 1024 and api._stream_smem(M, K, 1, 4) > 227 * 1024
                 continue
-            sk, blocks = plan
-            assert sk >= 1 and blocks >= sk
-            assert ((K + sk - 1) // sk + 15) // 16 * 16 <= 2560
+            sk, blocks, warps = plan
+            assert sk >= 1 and blocks >= sk and warps in (4, 8)
+            smem = api._stream_smem(M, K, sk, warps)
+            assert smem <= 227 * 1024
+            assert blocks == (2 * sms if warps == 4 and 2 * (smem + 1024) <= 228 * 1024 else sms)   # two blocks an SM only where two fit
             assert sk == 1 or (partial and mode != api.MODE_SILU)
+    # the hidden sizes of the three benchmark models at a batch of 8: whole rows of x in shared memory, the
+    # gated product and the float32 head included (no slices, so no fall-back to another kernel)
+    for K in (2560, 4096, 5120):
+        for mode in (api.MODE_SILU, api.MODE_STORE_F32, api.MODE_STORE):
+            sk, blocks, warps = api.stream_plan(8, 9728, K, mode)
+            assert sk == 1 and (warps, blocks) == ((4, 2 * sms) if K == 2560 else (8, sms))
 
 
 def test_skinny_tc_plan_gives_every_slice_work_and_no_more_units_than_sms():
@@ -28,7 +38,7 @@ def test_skinny_tc_plan_gives_every_slice_work_and_no_more_units_than_sms():
             assert sk >= 1 and (sk - 1) * ((kb + sk - 1) // sk) < kb          # no slice without a block of K
             assert sk == 1 or (mode == api.MODE_STORE and partial)
             if sk > 1:
-                assert ((N + bn - 1) // bn) * sk <= api.SM_COUNT
+                assert ((N + bn - 1) // bn) * sk <= api.sm_count()
     # the gated product of the benchmark model: the tile width that covers most SMs in one wave
     assert api.skinny_tc_plan(64, 9728, 2560, api.MODE_SILU) == (144, 1)
 
@@ -58,4 +68,4 @@ def test_the_tensor_core_product_is_picked_for_prefill_only_where_its_tiles_fill
     assert api.gemm_tc_fills_gpu(130, 640, 0.0)
     for M, N in itertools.product((129, 512, 2048, 8192, 32768), (640, 2560, 6144, 19456)):
         tiles = -(-M // 128) * -(-N // 256)
-        assert api.gemm_tc_fills_gpu(M, N) == (tiles / api.SM_COUNT / -(-tiles // api.SM_COUNT) >= 0.8)
+        assert api.gemm_tc_fills_gpu(M, N) == (tiles / api.sm_count() / -(-tiles // api.sm_count()) >= 0.8)

@@ -1,8 +1,10 @@
 """More toy parts defined here and registered from outside the library, mixed into one model layer
 by layer: a feed-forward with routing (top-1 of a few small experts), a position encoding of
-another form (rotation of interleaved pairs, applied by the part itself), and a norm of another
-kind (mean-centred, no weight on the mean). None of them is anyone's architecture; they show that
-the block, the schedule, the cache and the step function do not care what the parts are."""
+another form (rotation of interleaved pairs, applied by the part itself, after the attention
+part's per-head q/k norm), and a norm of another kind (mean-centred), which is also the first
+layer's input norm and the final norm, where the library would otherwise fuse its own RMSNorm into
+the embedding and the gather of the wanted rows. None of them is anyone's architecture; they show
+that the block, the schedule, the cache and the step function do not care what the parts are."""
 from dataclasses import dataclass
 
 import pytest
@@ -140,12 +142,12 @@ class ToyPartsConfig(dk.ModelConfig):
 
     def to_spec(self):
         H = self.hidden_size
-        attn = AttentionSpec(H, NH, NKV, HD, HD ** -0.5, None, PairRotarySpec(HD, self.theta), None)
+        attn = AttentionSpec(H, NH, NKV, HD, HD ** -0.5, RMSNormSpec(HD, self.eps), PairRotarySpec(HD, self.theta), None)
         ff = {"dense": GatedMLPSpec(H, self.intermediate_size), "routed": RoutedSpec(H, self.expert_size, self.n_experts)}
-        layers = tuple(LayerSpec(f"model.layers.{i}.", CentredNormSpec(H, self.eps) if i % 2 else RMSNormSpec(H, self.eps), attn,
+        layers = tuple(LayerSpec(f"model.layers.{i}.", RMSNormSpec(H, self.eps) if i % 2 else CentredNormSpec(H, self.eps), attn,
                                  RMSNormSpec(H, self.eps), ff[k]) for i, k in enumerate(self.feed_forwards))
         return ModelSpec(self.architecture, self.vocab_size, H, layers, ModelSpec.identity_schedule(len(layers)),
-                         RMSNormSpec(H, self.eps), True, 512)
+                         CentredNormSpec(H, self.eps), True, 512)
 
 
 def plain_forward(cfg, t, tokens):
@@ -154,9 +156,10 @@ def plain_forward(cfg, t, tokens):
     for i, kind in enumerate(cfg.feed_forwards):
         p = f"model.layers.{i}."
         w_in = t[p + "input_layernorm.weight"]
-        a = centred(h, w_in, cfg.eps) if i % 2 else plain.rms_norm(h, w_in, cfg.eps)
+        a = plain.rms_norm(h, w_in, cfg.eps) if i % 2 else centred(h, w_in, cfg.eps)
         q, k, v = plain.project_qkv(a, t[p + "self_attn.q_proj.weight"], t[p + "self_attn.k_proj.weight"],
                                     t[p + "self_attn.v_proj.weight"], NH, NKV, HD)
+        q, k = plain.rms_norm(q, t[p + "self_attn.q_norm.weight"], cfg.eps), plain.rms_norm(k, t[p + "self_attn.k_norm.weight"], cfg.eps)
         o = plain.causal_gqa_attention(pair_rotate(q, pos, cfg.theta), pair_rotate(k, pos, cfg.theta), v)
         h = h + o @ t[p + "self_attn.o_proj.weight"].T
         a = plain.rms_norm(h, t[p + "post_attention_layernorm.weight"], cfg.eps)
@@ -164,7 +167,7 @@ def plain_forward(cfg, t, tokens):
             h = h + plain.gated_mlp(a, t, p)
         else:
             h = h + routed(a, t[p + "mlp.router.weight"], t[p + "mlp.experts.up"], t[p + "mlp.experts.down"])
-    return plain.rms_norm(h, t["model.norm.weight"], cfg.eps) @ t["model.embed_tokens.weight"].T
+    return centred(h, t["model.norm.weight"], cfg.eps) @ t["model.embed_tokens.weight"].T
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

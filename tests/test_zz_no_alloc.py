@@ -60,3 +60,43 @@ def test_no_alloc_sampler_refuses_what_does_not_fit():
     err = lib.dk_sample_noalloc(None, 1, 8, t.data_ptr(), i.data_ptr(), i.data_ptr(), None, i.data_ptr(), 0, stream)
     assert err == -2
     torch.cuda.synchronize()
+
+
+def test_calls_back_to_back_on_the_same_positions_and_on_rows_without_alignment():
+    """Two calls in a row that advance the same positions, with programmatic dependent launch on (the
+    second call's first kernel may start while the first call's last kernel, which moves the positions on,
+    still runs): the second call draws at the advanced positions. And logits whose rows do not start on
+    16-byte boundaries (an offset view) are read with narrower loads, with the same result."""
+    lib = _lib()
+    lib.dk_set_pdl.argtypes = [c_int]
+    dev = "cuda"
+    n, V = 5, 8192 + 4
+    gen = torch.Generator().manual_seed(9)
+    buf = (torch.randn(n * V + 1, generator=gen) * 2).to(dev)
+    aligned, shifted = buf[:n * V].view(n, V), buf[1:].view(n, V)         # the second view starts 4 bytes off
+    temps = torch.full((n,), 0.9, device=dev)
+    seeds = torch.tensor([seed_words(77 + b) for b in range(n)], dtype=torch.int32, device=dev)
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    chunks = api.sample_chunks(V)
+    ws_v, ws_i = torch.empty(n * chunks, device=dev), torch.empty(n * chunks, dtype=torch.int32, device=dev)
+    lib.dk_set_pdl(1)
+    try:
+        for logits in (aligned, shifted):
+            pos = torch.tensor([3, 10, 0, 500, 64], dtype=torch.int32, device=dev)
+            first = torch.empty(n, dtype=torch.int32, device=dev)
+            second = torch.empty(n, dtype=torch.int32, device=dev)
+            for out in (first, second):
+                err = lib.dk_sample_noalloc(logits.data_ptr(), n, V, temps.data_ptr(), seeds.data_ptr(), pos.data_ptr(), None,
+                                            out.data_ptr(), 1, stream)
+                assert err == 0, lib.dk_sample_noalloc_error(err).decode()
+            torch.cuda.synchronize()
+            assert pos.tolist() == [5, 12, 2, 502, 66]
+            for k, out in enumerate((first, second)):                      # each call against the ordinary sampler at its positions
+                want = torch.empty(n, dtype=torch.int32, device=dev)
+                at = torch.tensor([3 + k, 10 + k, k, 500 + k, 64 + k], dtype=torch.int32, device=dev)
+                api.sample(logits.contiguous(), temps, seeds, at, None, ws_v, ws_i, want)
+                torch.cuda.synchronize()
+                assert out.tolist() == want.tolist(), (k, logits.data_ptr() % 16)
+            assert first.tolist() != second.tolist()                       # another position: other draws
+    finally:
+        lib.dk_set_pdl(0)
