@@ -57,13 +57,13 @@ def tolerance(dtype, ref):
     return (2e-4 if dtype == "float32" else 6e-2) * scale
 
 
-def run_trace(folder, dtype, out_dir, max_tokens, steps):
+def run_trace(folder, dtype, out_dir, max_tokens, steps, extra=()):
     """Runs bin/trace_run on ``steps`` (list of dicts); returns {step: float32 array [wanted, vocab]}."""
     import json
 
     vocab = json.load(open(os.path.join(folder, "config.json")))["vocab_size"]
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
-                           "--out", out_dir, "--max-tokens", str(max_tokens)],
+                           "--out", out_dir, "--max-tokens", str(max_tokens), *extra],
                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
                           timeout=900)
     assert proc.returncode == 0, proc.stderr[-4000:]

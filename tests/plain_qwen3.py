@@ -142,13 +142,15 @@ def decoder_layer(h, t, i, sz, window=None, kv_from=None):
     return h + gated_mlp(a, t, p), kv
 
 
-def forward(cfg, t, tokens, schedule=None):
+def forward(cfg, t, tokens, schedule=None, hidden_out=None):
     """Logits [S, V] of one whole sequence at every position: embedding gather without scaling
     (engine/engine.py:467), the layers in schedule order, final norm, lm_head, which is the
     embedding matrix when ``lm_head.weight`` is absent (engine/engine.py:290,498).
 
     ``schedule``: list of (layer, cache_entry, writes) triples; an entry with writes=False reads
-    the keys and values that the entry owning ``cache_entry`` produced. Default: each layer once."""
+    the keys and values that the entry owning ``cache_entry`` produced. Default: each layer once.
+    ``hidden_out``: a list that receives the residual stream [S, H] after every schedule entry (the
+    reference's ``_trace`` hook, engine/engine.py:496-497)."""
     sz = sizes(cfg)
     windows = layer_windows(cfg)
     if schedule is None:
@@ -159,6 +161,8 @@ def forward(cfg, t, tokens, schedule=None):
         h, kv = decoder_layer(h, t, layer, sz, windows[layer], None if writes else kvs[entry])
         if writes:
             kvs[entry] = kv
+        if hidden_out is not None:
+            hidden_out.append(h)
     a = rms_norm(h, t["model.norm.weight"], sz["eps"])
     head = t.get("lm_head.weight", t["model.embed_tokens.weight"])
     return a @ head.T

@@ -86,3 +86,36 @@ def test_decode_steps_at_full_width_agree_with_float32(batch):
     assert got.shape == (4, batch, cfg.vocab_size)
     err = float((got - want).abs().max())
     assert err <= 0.03 * scale, f"{err} against float32 logits of size {scale}"
+
+
+@pytest.mark.parametrize("hidden,inter,heads", [(2560, 9728, 32), (2816, 5008, 24)])
+def test_full_width_against_the_plain_implementation(tmp_path, hidden, inter, heads):
+    """Two layers at the benchmark model's widths (and at a hidden size above them, where the streaming
+    product keeps the longer rows of x in blocks of eight streaming warps), float32 and bfloat16, short ragged prompts with logits
+    at two places each and then decode steps of the batch, against the plain implementation on the CPU:
+    not against the library's own float32 path, so a fault the two dtypes share would show."""
+    import plain_qwen3 as plain
+    cfg = dk.config_from_dict(dict(WIDTHS, hidden_size=hidden, intermediate_size=inter, num_attention_heads=heads))
+    folder = dk.write_random_model(cfg, str(tmp_path / "wide"), seed=4, dtype=torch.bfloat16, matrix_std=0.02)
+    pcfg, t = plain.read_model(folder)
+    rs = np.random.RandomState(11)
+    lens, extra = (129, 300, 70), 3
+    seqs = [rs.randint(0, cfg.vocab_size, n + extra).tolist() for n in lens]
+    want = []
+    for s, n in zip(seqs, lens):
+        ref = plain.forward(pcfg, t, s)
+        want.append(ref[[n // 2, n - 1] + list(range(n, n + extra))])
+    scale = max(float(w.abs().max()) for w in want)
+    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 0.03)):
+        runner = dk.Runner(dk.load_model(folder, dtype), sum((len(s) + 63) // 64 * 64 for s in seqs), max_slots=3)
+        slots = [runner.begin() for _ in seqs]
+        got = [runner.step([(sl, s[:n], [n // 2, n - 1]) for sl, s, n in zip(slots, seqs, lens)]).float().cpu().view(3, 2, -1)]
+        for k in range(extra):
+            got.append(runner.step([(sl, [s[n + k]], [0]) for sl, s, n in zip(slots, seqs, lens)]).float().cpu().view(3, 1, -1))
+        torch.cuda.synchronize()
+        api.gemm_tc_check()
+        got = torch.cat(got, 1)
+        for i in range(3):
+            err = float((got[i] - want[i]).abs().max())
+            assert err <= tol * scale, f"{dtype} request {i}: {err} against plain logits of size {scale}"
+        del runner

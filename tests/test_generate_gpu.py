@@ -125,33 +125,6 @@ def test_engine_refuses_bad_input(tmp_path):
     assert len(list(small.generate([[1] * 10], 5))) == 5
 
 
-def test_products_that_add_into_the_residual_and_apply_the_deferred_norm(tmp_path, monkeypatch):
-    """The optional decode path without add+norm launches (parts opt in with fuses_residual) gives
-    the plain implementation's tokens too, and really runs the fused kernels."""
-    from dryft_challenge_htn_2026_b200.csrc import api
-    from dryft_challenge_htn_2026_b200.parts.attention import GQAAttention
-    from dryft_challenge_htn_2026_b200.parts.feedforward import GatedMLP
-    folder = make_folder(tmp_path, "D", seed=12)
-    cfg, t = plain.read_model(folder)
-    prompts = [random_tokens(TINY["D"]["vocab_size"], L, 40 + i) for i, L in enumerate([4, 70, 33])]
-    monkeypatch.setattr(GQAAttention, "fuses_residual", True)
-    monkeypatch.setattr(GatedMLP, "fuses_residual", True)
-    seen = {"residual": 0, "deferred": 0}
-    inner = api.gemv_stream
-
-    def counting(x, w, out=None, mode=api.MODE_STORE, plan=None, residual=None, prefetch=None):
-        seen["residual"] += residual is not None
-        seen["deferred"] += isinstance(x, api.Normed)
-        return inner(x, w, out, mode, plan, residual, prefetch)
-
-    monkeypatch.setattr(api, "gemv_stream", counting)
-    steps = list(dk.Engine(folder, dtype=torch.bfloat16, use_graph=False).generate(prompts, 16))
-    assert seen["residual"] > 0 and seen["deferred"] > 0
-    scale = max(1.0, float(plain.forward(cfg, t, prompts[1]).abs().max()))
-    for i, p in enumerate(prompts):
-        assert teacher_forced_gap(cfg, t, p, [s[i] for s in steps]) <= 0.12 * scale
-
-
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_prefill_projection_with_norm_rotation_and_cache_write_in_its_epilogue(tmp_path, monkeypatch, name):
     """Prefill steps of more than 128 rows whose q/k/v projection norms, rotates and writes the cache
@@ -187,13 +160,20 @@ def test_prefill_in_several_steps_gives_the_same_tokens(tmp_path):
     whole = list(dk.Engine(folder, dtype=torch.float32).generate(prompts, 10, temperature=0.8, seed=4))
     pieces = list(dk.Engine(folder, dtype=torch.float32, max_prefill_tokens=50).generate(prompts, 10, temperature=0.8, seed=4))
     assert pieces == whole
+    # bfloat16: continuation chunks on top of a cache, a last portion of one token (51 under a limit of 50) and
+    # of two (52), steps of few rows through the skinny products, windowed layers after trimming
+    cfg, t = plain.read_model(folder)
+    prompts.append(random_tokens(TINY["C"]["vocab_size"], 52, 77))
     bf = list(dk.Engine(folder, dtype=torch.bfloat16, max_prefill_tokens=50).generate(prompts, 10))
     assert len(bf) == 10 and all(len(s) == len(prompts) for s in bf)
+    scale = max(1.0, float(plain.forward(cfg, t, prompts[2]).abs().max()))
+    for i, p in enumerate(prompts):
+        assert teacher_forced_gap(cfg, t, p, [s[i] for s in bf]) <= 0.12 * scale, i
 
 
 def test_twenty_sequences_decode_on_the_tensor_core_product(tmp_path):
-    """A batch beyond 8 rows takes the tcgen05 decode product (32-row decode state here, 12 of the
-    rows padding after some sequences stop): tokens stay within rounding of the plain implementation."""
+    """A batch beyond 8 rows takes the tcgen05 decode product (a 32-row decode state here, 12 of the
+    rows padding): tokens stay within rounding of the plain implementation."""
     folder = make_folder(tmp_path, "D", seed=14)
     cfg, t = plain.read_model(folder)
     prompts = [random_tokens(TINY["D"]["vocab_size"], 3 + (7 * i) % 60, 80 + i) for i in range(20)]
@@ -203,3 +183,48 @@ def test_twenty_sequences_decode_on_the_tensor_core_product(tmp_path):
     scale = max(1.0, float(plain.forward(cfg, t, prompts[5]).abs().max()))
     for i in (0, 5, 11, 19):
         assert teacher_forced_gap(cfg, t, prompts[i], [s[i] for s in steps]) <= 0.12 * scale
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_stop_tokens_repack_into_a_smaller_graph(tmp_path, dtype):
+    """Greedy generation of 11 sequences under CUDA graphs with stop tokens chosen so that sequences
+    end at different steps: the batch is re-packed into smaller decode states (16 -> 8 -> 4 rows, a new
+    graph each), and what every sequence emits up to its stop is what it emits without stops."""
+    folder = make_folder(tmp_path, "D", seed=16)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY["D"]["vocab_size"], 5 + (11 * i) % 70, 300 + i) for i in range(11)]
+    eng = dk.Engine(folder, dtype=dtype)
+    free = list(eng.generate(prompts, 24))
+    streams = [[s[i] for s in free] for i in range(len(prompts))]
+    # stop tokens: what sequence i emits at step 3 + 2 i (for the first eight), so the batch shrinks again and again
+    stops = {streams[i][3 + 2 * i] for i in range(8)}
+    rows = list(eng.generate(prompts, 24, stop_token_ids=sorted(stops)))
+    ended = 0
+    for i, full in enumerate(streams):
+        got = [r[i] for r in rows if r[i] is not None]
+        cut = next((k for k, tok in enumerate(full) if tok in stops), len(full) - 1)
+        if dtype == torch.float32:
+            assert got == full[:cut + 1], i
+        else:       # bfloat16: another decode state takes other product kernels; compare with the plain implementation
+            assert len(got) >= 1 and (got[-1] in stops or len(got) == 24)
+            scale = max(1.0, float(plain.forward(cfg, t, prompts[i]).abs().max()))
+            assert teacher_forced_gap(cfg, t, prompts[i], got) <= 0.12 * scale, i
+        ended += got[-1] in stops
+    assert ended >= 8
+    states = eng.backend.loop.states
+    assert len({rows_ for rows_, _ in states}) >= 3                   # several bucket sizes were used
+
+
+def test_a_decode_step_of_more_than_128_sequences(tmp_path):
+    """150 sequences in one batch: the decode state has 256 rows, beyond what the decode forms of the
+    products take, so its steps run the prefill forms (and the library product) on one token a row."""
+    folder = make_folder(tmp_path, "D", seed=17)
+    cfg, t = plain.read_model(folder)
+    prompts = [random_tokens(TINY["D"]["vocab_size"], 2 + (5 * i) % 40, 500 + i) for i in range(150)]
+    for dtype, bound in ((torch.float32, 1e-4), (torch.bfloat16, None)):
+        steps = list(dk.Engine(folder, dtype=dtype).generate(prompts, 6))
+        assert len(steps) == 6 and all(len(s) == 150 for s in steps)
+        for i in (0, 7, 64, 128, 149):
+            scale = max(1.0, float(plain.forward(cfg, t, prompts[i]).abs().max()))
+            gap = teacher_forced_gap(cfg, t, prompts[i], [s[i] for s in steps])
+            assert gap <= (bound if bound is not None else 0.12 * scale), (dtype, i, gap)
