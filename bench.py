@@ -178,20 +178,23 @@ def time_decode(torch, dk, model, cfg, size, batch, steps, warmup, seed):
 
 
 def time_prefill(torch, dk, model, cfg, tokens, iters=3):
+    """One prompt of ``tokens`` tokens through the step function as generation calls it (a step shape
+    that repeats is replayed as a CUDA graph): two untimed runs (plain, then the capture), then the
+    median of ``iters`` runs, each between synchronisations, timed with CUDA events."""
     import numpy as np
     runner = dk.Runner(model, tokens + 64, max_slots=2)
     prompt = np.random.RandomState(7).randint(0, model.spec.vocab_size, tokens).tolist()
     times = []
-    for i in range(iters + 1):
+    for i in range(iters + 2):
         slot = runner.begin()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        runner.step([(slot, prompt, [tokens - 1])])
+        runner.step([(slot, prompt, [tokens - 1])], graph=True)
         e1.record()
         torch.cuda.synchronize()
         runner.end(slot)
-        if i:
+        if i >= 2:
             times.append(e0.elapsed_time(e1))
     del runner
     torch.cuda.empty_cache()
@@ -270,7 +273,8 @@ def run_ours(args):
                 points[f"decode_b{b}"] = detail[f"decode_b{b}"]["value"]
         ms, flops = time_prefill(torch, dk, model, cfg_d, PREFILL_TOKENS)
         prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
-                   "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                   "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "short_ms": {str(n): round(time_prefill(torch, dk, model, cfg_d, n)[0], 3) for n in (128, 512)}}
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
     out = {
         "metric": f"decode tok/s at batch {args.batch} ({SIZES[size]['name']}, bf16)", "value": round(main_run["tok_s"], 1),

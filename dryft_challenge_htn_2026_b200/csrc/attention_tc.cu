@@ -57,7 +57,20 @@ constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms acr
 constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;   // Q tile; one stage of K or of V
 constexpr int Q_ATOM_BYTES = BM * 128;            // the 128 query rows of one 64-column atom
 constexpr int KV_ATOM_BYTES = BN * 128;           // the key rows of one 64-column atom
-constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
+#ifndef DK_WAIT_CYCLES
+#define DK_WAIT_CYCLES 2000000000LL               // about a second: a wait this long has failed
+#endif
+constexpr long long WAIT_CYCLES = DK_WAIT_CYCLES;
+#ifdef DK_TEST_STALL
+// Test build only: with the flag set the loader thread requests nothing, so the waits of the mma
+// thread and the softmax warps run out (after DK_WAIT_CYCLES, which such a build makes short) and
+// the error path runs: code in *err, tensor memory freed, kernel returns.
+__device__ int dk_stall_flag;
+DK_EXPORT int dk_test_stall(int on) { return (int)cudaMemcpyToSymbol(dk_stall_flag, &on, sizeof(int)); }
+#define DK_STALLED (dk_stall_flag != 0)
+#else
+#define DK_STALLED false
+#endif
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
@@ -286,7 +299,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // Step j of the item is step t = step + j of the block; it uses stage / buffer / barrier t & 1, whose
     // barriers are then in their phase (t >> 1) & 1.
     if (warp == LOAD_WARP) {
-        if (lane == 0) {  // ---------------------------------------------------------- loader: every TMA
+        if (lane == 0 && DK_STALLED) item_slot[1] = 1;      // (test build) nothing is requested: the others' waits run out
+        if (lane == 0 && !DK_STALLED) {  // ------------------------------------------- loader: every TMA
             load_q(cur);
             load_kv(&map_k, k_s, bar_k, cur, step, 0);
             load_kv(&map_v, v_s, bar_v, cur, step, 0);

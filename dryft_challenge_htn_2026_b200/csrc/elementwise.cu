@@ -71,10 +71,11 @@ __global__ void add_rmsnorm_kernel(float* h, const T* delta, const float* parts,
     for (int i = threadIdx.x; i < H; i += blockDim.x) ar[i] = from_f<T>(src[i] * rs * w[i]);
 }
 
-// The same for few rows (decode), built for latency: one block per row, one thread per 4 columns,
-// values kept in registers between the two passes, every load of a pass requested before any is
-// used, and what never comes from the kernel before this one (norm weight, row index) fetched
-// before the wait for it. H % 4 == 0, H <= 4096.
+// The same for few rows (decode, and short prefill steps whose products leave partial sums), built
+// for latency: one block per row, one or two groups of 4 columns a thread, values kept in registers
+// between the two passes, every load of a pass requested before any is used, and what never comes
+// from the kernel before this one (norm weight, row index) fetched before the wait for it.
+// H % 4 == 0, H <= 8192.
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ld4(const bf16* p) {
     const uint2 v = *reinterpret_cast<const uint2*>(p);
@@ -90,38 +91,54 @@ __device__ __forceinline__ void st4(bf16* p, float4 v) {
     o.y = *reinterpret_cast<uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(p) = o;
 }
-template <typename T>
+template <typename T, int QPT>
 __global__ void add_rmsnorm_quad_kernel(float* h, const T* delta, const float* parts, int n_parts, size_t part_stride,
                                         const int* rows, const float* __restrict__ w, float eps, int H, T* a) {
     __shared__ float red[33];
-    const int c = threadIdx.x * 4;
-    const bool on = c < H;
+    // QPT groups of 4 columns a thread: group q of thread t is columns 4 * (t + q * blockDim.x) ...
     const size_t out_row = blockIdx.x;
     const size_t row = rows ? (size_t)rows[out_row] : out_row;
-    const float4 w4 = on ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 w4[QPT];
+#pragma unroll
+    for (int q = 0; q < QPT; q++) {
+        const int c = (threadIdx.x + q * blockDim.x) * 4;
+        w4[q] = c < H ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
     pdl_launch_dependents();
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (on) {
-        v = ld4(h + row * H + c);
-        if (delta) {
-            const float4 d = ld4(delta + row * H + c);
-            v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
-        }
-        if (parts) {
-            float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-            for (int k = 0; k < n_parts; k++) {
-                const float4 p = ld4(parts + (size_t)k * part_stride + row * H + c);
-                d.x += p.x, d.y += p.y, d.z += p.z, d.w += p.w;
+    float4 v[QPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int q = 0; q < QPT; q++) {
+        const int c = (threadIdx.x + q * blockDim.x) * 4;
+        v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < H) {
+            v[q] = ld4(h + row * H + c);
+            if (delta) {
+                const float4 d = ld4(delta + row * H + c);
+                v[q].x += d.x, v[q].y += d.y, v[q].z += d.z, v[q].w += d.w;
             }
-            v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+            if (parts) {
+                float4 d = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+                for (int k = 0; k < n_parts; k++) {
+                    const float4 p = ld4(parts + (size_t)k * part_stride + row * H + c);
+                    d.x += p.x, d.y += p.y, d.z += p.z, d.w += p.w;
+                }
+                v[q].x += d.x, v[q].y += d.y, v[q].z += d.z, v[q].w += d.w;
+            }
+            if (!rows && (delta || parts)) st4(h + row * H + c, v[q]);
         }
-        if (!rows && (delta || parts)) st4(h + row * H + c, v);
+        ss += v[q].x * v[q].x + v[q].y * v[q].y + v[q].z * v[q].z + v[q].w * v[q].w;
     }
-    const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+    ss = block_sum(ss, red);
     const float rs = rsqrtf(ss / (float)H + eps);
-    if (on) st4(a + out_row * H + c, make_float4(v.x * rs * w4.x, v.y * rs * w4.y, v.z * rs * w4.z, v.w * rs * w4.w));
+#pragma unroll
+    for (int q = 0; q < QPT; q++) {
+        const int c = (threadIdx.x + q * blockDim.x) * 4;
+        if (c < H)
+            st4(a + out_row * H + c, make_float4(v[q].x * rs * w4[q].x, v[q].y * rs * w4[q].y, v[q].z * rs * w4[q].z, v[q].w * rs * w4[q].w));
+    }
 }
 
 // out[r, c] = silu(gu[r, c]) * gu[r, I + c],  gu rows are [gate | up] of width 2*I
@@ -501,8 +518,12 @@ DK_EXPORT int dk_add_rmsnorm(int dtype, float* h, const void* delta, const float
     if (dtype == 1 && parts == nullptr && rows == nullptr && H % 8 == 0 && H <= 8 * 4 * row_threads(H) && n_rows > 64)
         return dk_launch(add_rmsnorm_wide_kernel, dim3(n_rows), dim3(row_threads(H)), 0, st, h, (const bf16*)delta, w, eps,
                          H, (bf16*)a);
-    if (n_rows <= 64 && H % 4 == 0 && H <= 4096 && part_stride % 4 == 0) {
-        DISPATCH_T(dtype, return dk_launch(add_rmsnorm_quad_kernel<T>, dim3(n_rows), dim3((H / 4 + 31) / 32 * 32), 0, st, h,
+    if ((n_rows <= 64 || parts != nullptr) && H % 4 == 0 && H <= 8192 && part_stride % 4 == 0) {
+        if (H <= 4096) {
+            DISPATCH_T(dtype, return dk_launch(add_rmsnorm_quad_kernel<T, 1>, dim3(n_rows), dim3((H / 4 + 31) / 32 * 32), 0, st, h,
+                                               (const T*)delta, parts, n_parts, (size_t)part_stride, rows, w, eps, H, (T*)a));
+        }
+        DISPATCH_T(dtype, return dk_launch(add_rmsnorm_quad_kernel<T, 2>, dim3(n_rows), dim3((H / 8 + 31) / 32 * 32), 0, st, h,
                                            (const T*)delta, parts, n_parts, (size_t)part_stride, rows, w, eps, H, (T*)a));
     }
     size_t smem = rows ? (size_t)H * sizeof(float) : 0;

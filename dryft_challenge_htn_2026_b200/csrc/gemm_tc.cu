@@ -36,7 +36,20 @@ namespace {
 constexpr int BM = 128, BK = 64;
 constexpr int A_BYTES = BM * BK * 2;     // what the mma reads of x per stage: 128 rows of 128 bytes
 constexpr int MAX_STAGES = 12;
-constexpr long long WAIT_CYCLES = 2000000000LL;   // about a second: a wait this long has failed
+#ifndef DK_WAIT_CYCLES
+#define DK_WAIT_CYCLES 2000000000LL               // about a second: a wait this long has failed
+#endif
+constexpr long long WAIT_CYCLES = DK_WAIT_CYCLES;
+#ifdef DK_TEST_STALL
+// Test build only: with the flag set the producer requests nothing, so every wait of the other
+// roles runs out (after DK_WAIT_CYCLES, which such a build makes short) and the error path runs:
+// code in *err, tensor memory freed, kernel returns.
+__device__ int dk_stall_flag;
+DK_EXPORT int dk_test_stall(int on) { return (int)cudaMemcpyToSymbol(dk_stall_flag, &on, sizeof(int)); }
+#define DK_STALLED (dk_stall_flag != 0)
+#else
+#define DK_STALLED false
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -276,7 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        if (lane == 0) {  // ------------------------------------------------------------ producer
+        if (lane == 0 && !DK_STALLED) {  // ---------------------------------------------- producer
             int it = 0;   // stages issued so far, over all units of this block
             int s = 0;    // it % STAGES, and round = (it / STAGES) & 1, kept by counting (no division on this path)
             uint32_t round = 0;

@@ -41,8 +41,10 @@ class StepContext:
         return self._scratch[key]
 
 
-def _pack(arrays, device):
-    """One pinned int32 buffer, one copy, views per array (each 16-byte aligned)."""
+def _pack(arrays, device, static=None):
+    """One pinned int32 buffer, one copy, views per array (each 16-byte aligned). ``static``: a dict
+    that keeps the device buffer between calls, so that steps of the same shape find their arrays
+    at the same addresses (a captured graph reads them there)."""
     offs, total = [], 0
     for a in arrays:
         offs.append(total)
@@ -51,15 +53,25 @@ def _pack(arrays, device):
     hn = host.numpy()
     for a, o in zip(arrays, offs):
         hn[o:o + a.size] = a.reshape(-1)
-    dev = host.to(device, non_blocking=True)
+    if static is None:
+        dev = host.to(device, non_blocking=True)
+    else:
+        if "dev" not in static:
+            static["dev"] = torch.empty(host.numel(), dtype=torch.int32, device=device)
+        dev = static["dev"]
+        if dev.numel() != host.numel():
+            raise ValueError("a step context of another shape than the one its static buffer was made for")
+        dev.copy_(host, non_blocking=True)
+        static["host"] = host                  # pinned memory must outlive the copy
     return [dev[o:o + a.size].view(a.shape) for a, o in zip(arrays, offs)]
 
 
-def build_context(cache, entries, device, scratch_store=None, pad_to=None, plans=()):
+def build_context(cache, entries, device, scratch_store=None, pad_to=None, plans=(), static=None):
     """``entries``: list of (slot, tokens, want) with ``want`` positions among these tokens.
     Reserves cache room for the new tokens. ``pad_to``: for decode steps, pad the batch with rows
     of position -1 up to this many rows (a captured graph has a fixed size). ``plans``: the
-    ``StepPlan`` objects of the model's parts; each is built once and uploaded with the rest."""
+    ``StepPlan`` objects of the model's parts; each is built once and uploaded with the rest.
+    ``static``: see ``_pack``."""
     n_seq = len(entries)
     lens = np.array([len(e[1]) for e in entries], dtype=np.int64)
     if n_seq == 0 or (lens < 1).any():
@@ -100,7 +112,7 @@ def build_context(cache, entries, device, scratch_store=None, pad_to=None, plans
         if p.key not in by_key:
             by_key[p.key] = i32(p.build(lens, pos0, is_decode))
     fixed = [i32(tok), i32(row_seq), i32(row_pos), i32(cu), i32(slots), i32(pos0), i32(want)]
-    dev = _pack(fixed + tables + list(by_key.values()), device)
+    dev = _pack(fixed + tables + list(by_key.values()), device, static)
     ctx = StepContext(scratch_store)
     ctx.n_tok, ctx.n_seq, ctx.n_want, ctx.is_decode = rows, n_seq, len(want), is_decode
     ctx.max_position = int((pos0 + lens).max()) - 1

@@ -91,6 +91,28 @@ def plan_batches(n_requests, batch_size):
     return [range(s, min(n_requests, s + batch_size)) for s in range(0, n_requests, batch_size)]
 
 
+def prefill_plan(lengths, limit):
+    """Steps of a batch's prefill: each a list of (sequence, first token, end token). Whole sequences
+    are taken in order while they fit ``limit`` tokens; a longer one is cut into chunks."""
+    limit = max(1, limit)
+    steps, cur, used = [], [], 0
+    for i, n in enumerate(lengths):
+        if n > limit:
+            if cur:
+                steps.append(cur)
+                cur, used = [], 0
+            steps += [[(i, p0, min(n, p0 + limit))] for p0 in range(0, n, limit)]
+            continue
+        if used + n > limit:
+            steps.append(cur)
+            cur, used = [], 0
+        cur.append((i, 0, n))
+        used += n
+    if cur:
+        steps.append(cur)
+    return steps
+
+
 def bucket_rows(n):
     """Rows of the decode state for n live sequences: the next power of two (a captured graph has
     a fixed size; padding rows are skipped by the kernels)."""
@@ -228,16 +250,16 @@ class DecodeLoop:
     def __init__(self, runner, use_graph=True):
         self.runner, self.use_graph = runner, use_graph
         self.states = {}
-        self.prepared = 0
+        self.generation = runner.model.generation
         self.state = None
 
     def state_for(self, n_live, max_len):
         """The decode state for ``n_live`` sequences that will grow to at most ``max_len`` tokens."""
         rows = bucket_rows(n_live)
         width = bucket_rows((max_len + PAGE - 1) // PAGE)
-        if max_len > self.prepared:           # position tables grow: graphs captured before are stale
-            self.prepared = max(max_len, 2 * self.prepared)
-            self.runner.model.prepare(self.prepared)
+        generation = self.runner.model.prepare(max_len)
+        if generation != self.generation:     # position tables were rebuilt: graphs captured before are stale
+            self.generation = generation
             self.states.clear()
         st = self.states.get((rows, width))
         if st is None:
@@ -271,7 +293,7 @@ class DecodeLoop:
         st = self.state
         max_len = max(cache.length[slot] for slot, _, _ in entries) + 1
         if st is None or st.filled != now or st.lengths != [cache.length[slot] for slot, _, _ in entries] \
-                or st.width * PAGE < max_len or max_len > self.prepared:
+                or st.width * PAGE < max_len or self.runner.model.prepare(max_len) != self.generation:
             st = self.state_for(len(entries), max_len)
             st.fill([dict(slot=slot, token=tokens[0], pos=cache.length[slot], temperature=0.0, seed=0)
                      for slot, tokens, _ in entries])
@@ -297,27 +319,6 @@ class GpuBackend:
     def state(self):
         return self.loop.state
 
-    def _prefill_plan(self, lengths):
-        """Steps of the prefill: each a list of (sequence, first token, end token). Whole sequences
-        are taken in order while they fit ``max_prefill_tokens``; a longer one is cut into chunks."""
-        limit = max(1, self.max_prefill_tokens)
-        steps, cur, used = [], [], 0
-        for i, n in enumerate(lengths):
-            if n > limit:
-                if cur:
-                    steps.append(cur)
-                    cur, used = [], 0
-                steps += [[(i, p0, min(n, p0 + limit))] for p0 in range(0, n, limit)]
-                continue
-            if used + n > limit:
-                steps.append(cur)
-                cur, used = [], 0
-            cur.append((i, 0, n))
-            used += n
-        if cur:
-            steps.append(cur)
-        return steps
-
     @torch.inference_mode()
     def start(self, prompts, params, seeds):
         r = self.runner
@@ -336,11 +337,11 @@ class GpuBackend:
         self.max_len = max(len(p) for p in prompts) + params.max_new_tokens
         st = self.loop.state_for(len(prompts), self.max_len)
         st.fill(self.seqs)
-        for step in self._prefill_plan([len(p) for p in prompts]):
+        for step in prefill_plan([len(p) for p in prompts], self.max_prefill_tokens):
             # logits only where a prompt ends; the first token of those sequences is sampled at once
             ended = [i for i, _, p1 in step if p1 == len(prompts[i])]
             logits, ctx = r.step([(slots[i], prompts[i][p0:p1], [p1 - p0 - 1] if p1 == len(prompts[i]) else [])
-                                  for i, p0, p1 in step], with_context=True)
+                                  for i, p0, p1 in step], with_context=True, graph=self.loop.use_graph)
             if ended:
                 lo, hi = ended[0], ended[-1] + 1          # sequences are taken in order: a contiguous range
                 st.sampler(logits, st.temps[lo:hi], st.seeds[lo:hi], ctx.row_pos, ctx.want_rows, st.ctx.tok[lo:hi], False)

@@ -38,6 +38,8 @@ class CausalLM:
         self.tied = None
         # index arrays the parts' kernels want built for every step (engine.batch.build_context), once per key
         self.step_plans = list({p.key: p for b in self.blocks for p in b.step_plans()}.values())
+        self.prepared = 0        # positions the parts' tables reach
+        self.generation = 0      # counts the times they were rebuilt: captured graphs hold the old tables' addresses
 
     # -- parameters --------------------------------------------------------------------------
     def param_decls(self, tied):
@@ -68,8 +70,14 @@ class CausalLM:
         return self._entry_requests
 
     def prepare(self, max_positions):
-        for b in self.blocks:
-            b.prepare(max_positions)
+        """Makes the parts' tables (rotation angles) reach ``max_positions``; they grow by doubling.
+        Returns ``generation``, which changes whenever they were rebuilt."""
+        if max_positions > self.prepared:
+            self.prepared = max(max_positions, 2 * self.prepared, 256)
+            for b in self.blocks:
+                b.prepare(self.prepared)
+            self.generation += 1
+        return self.generation
 
     def weight_bytes_per_step(self):
         """Bytes of weights a decode step reads: what every part says it streams once a step, for

@@ -242,8 +242,8 @@ def test_request_seeds_are_distinct_and_fit_two_words():
 
 
 def test_prefill_plan_groups_whole_sequences_and_chunks_long_ones():
-    from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
-    plan = GpuBackend(None, max_prefill_tokens=100)._prefill_plan
+    from dryft_challenge_htn_2026_b200.engine.generate import prefill_plan
+    plan = lambda lengths: prefill_plan(lengths, 100)
     assert plan([10, 20, 30]) == [[(0, 0, 10), (1, 0, 20), (2, 0, 30)]]
     assert plan([60, 50, 40, 100]) == [[(0, 0, 60)], [(1, 0, 50), (2, 0, 40)], [(3, 0, 100)]]
     assert plan([30, 250, 5]) == [[(0, 0, 30)], [(1, 0, 100)], [(1, 100, 200)], [(1, 200, 250)], [(2, 0, 5)]]

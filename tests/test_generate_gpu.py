@@ -228,3 +228,29 @@ def test_a_decode_step_of_more_than_128_sequences(tmp_path):
             scale = max(1.0, float(plain.forward(cfg, t, prompts[i]).abs().max()))
             gap = teacher_forced_gap(cfg, t, prompts[i], [s[i] for s in steps])
             assert gap <= (bound if bound is not None else 0.12 * scale), (dtype, i, gap)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prefill_steps_replayed_as_graphs_give_the_same_tokens(tmp_path, dtype):
+    """A prompt shape that comes a second time is captured and from then on replayed (the first time it
+    runs plainly): the same tokens as without graphs, also for other prompts of that shape on other
+    slots, for a shape captured earlier that returns, and for prompts in several steps."""
+    folder = make_folder(tmp_path, "D", seed=18)
+    vocab = TINY["D"]["vocab_size"]
+    lens = [150, 40, 3, 64]
+    plain_eng = dk.Engine(folder, dtype=dtype, use_graph=False)
+    eng = dk.Engine(folder, dtype=dtype, use_graph=True)
+    for round_ in range(4):
+        prompts = [random_tokens(vocab, L, 700 + 10 * round_ + i) for i, L in enumerate(lens)]
+        if round_ == 3:
+            prompts = prompts[::-1]                                    # another shape in between
+        want = list(plain_eng.generate(prompts, 5, temperature=0.7, seed=round_))
+        assert list(eng.generate(prompts, 5, temperature=0.7, seed=round_)) == want, round_
+    assert len(eng.runner._graphs) == 1                               # the shape that came more than once
+    prompts = [random_tokens(vocab, L, 800 + i) for i, L in enumerate(lens)]
+    assert list(eng.generate(prompts, 5)) == list(plain_eng.generate(prompts, 5))     # the captured shape again, after another
+    chunked = dk.Engine(folder, dtype=dtype, use_graph=True, max_prefill_tokens=100)
+    want = list(dk.Engine(folder, dtype=dtype, use_graph=False, max_prefill_tokens=100).generate(prompts, 5))
+    for _ in range(3):                                                 # steps of 100 + 50 | 40 + 3 | 64 tokens, each shape captured
+        assert list(chunked.generate(prompts, 5)) == want
+    assert len(chunked.runner._graphs) >= 3

@@ -43,7 +43,7 @@ def test_embed_rmsnorm(dtype, T, H, V):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,H", [(1, 64), (33, 2560), (70, 200), (130, 2560), (67, 512), (100, 4096)])
+@pytest.mark.parametrize("T,H", [(1, 64), (33, 2560), (70, 200), (130, 2560), (67, 512), (100, 4096), (8, 5120), (40, 8192), (3, 8200)])
 def test_add_rmsnorm_and_row_gather(dtype, T, H):
     h0, delta, w = rnd(T, H, seed=3, scale=3.0), rnd(T, H, dtype=dtype, seed=4), 1 + 0.1 * rnd(H, seed=5)
     h = h0.clone()
@@ -61,6 +61,12 @@ def test_add_rmsnorm_and_row_gather(dtype, T, H):
     api.add_rmsnorm(h, delta, w, 1e-6, ag, rows)
     assert torch.equal(h, h0)                                             # gathering leaves h alone
     close(ag, rms(ref_h[rows.long()], w, 1e-6), dtype, "gathered add_rmsnorm")
+    # split-K partial sums in place of the delta (every row count takes the few-rows kernel then, up to 8,192 columns)
+    parts = rnd(3, T, H, seed=6)
+    h = h0.clone()
+    api.add_rmsnorm(h, api.Partial(parts), w, 1e-6, a)
+    assert torch.allclose(h, h0 + parts.sum(0), atol=1e-5)
+    close(a, rms(h0 + parts.sum(0), w, 1e-6), dtype, "add_rmsnorm(partial sums)")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -170,7 +176,7 @@ def test_qk_norm_rope_write(dtype, nh, nkv, hd):
     close(d[:, :nh][keep], rms(x[:, :nh], qn, 1e-6)[keep], dtype, "dense q")
     close(d[:, nh:nh + nkv][keep], rms(x[:, nh:nh + nkv], kn, 1e-6)[keep], dtype, "dense k")
     assert torch.equal(d[:, nh + nkv:][keep], qkv.view(T, nh + 2 * nkv, hd)[:, nh + nkv:][keep])
-    assert torch.equal(s["k_store"], k_before) and torch.equal(q_out, q_before) and float(dense[4].abs().sum()) == 0
+    assert torch.equal(s["k_store"], k_before) and torch.equal(q_out[keep], q_before[keep]) and float(dense[4].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
