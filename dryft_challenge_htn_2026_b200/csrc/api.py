@@ -528,7 +528,7 @@ def gemm_tc_fills_gpu(M, N, min_fill=0.8):
 
 
 def gemm_tc_check():
-    """Raises if a bounded wait inside gemm_tc ran out since the last check (synchronises)."""
+    """Raises if a bounded wait inside gemm_tc or attention_prefill_tc ran out since the last check (synchronises)."""
     if _tc_err is not None:
         code = int(_tc_err.item())
         if code:
@@ -565,3 +565,4 @@ def attention_prefill_tc(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page_t
                                        c_longlong(k_store.shape[0]), _p(tiles), tiles.shape[0], _p(cu_q), _p(seq_pos0),
                                        _p(page_table), page_table.shape[1], n_heads, n_kv_heads, int(window or 0),
                                        c_float(scale), _p(_tc_err), _p(sched), c_void_p(stream)), "attention_prefill_tc")
+

@@ -31,6 +31,11 @@ TINY = {
     "E": dict(vocab_size=264, hidden_size=96, intermediate_size=160, num_hidden_layers=3, num_attention_heads=3,
               num_key_value_heads=1, head_dim=128, rms_norm_eps=2e-6, rope_theta=20000.0, tie_word_embeddings=True,
               max_position_embeddings=1024, use_sliding_window=True, sliding_window=150, max_window_layers=1),
+    # what the others leave out in one model: head size 48 with a group of 3, an untied head and a window from the
+    # second layer on
+    "F": dict(vocab_size=272, hidden_size=80, intermediate_size=112, num_hidden_layers=3, num_attention_heads=6,
+              num_key_value_heads=2, head_dim=48, rms_norm_eps=1e-5, rope_theta=300000.0, tie_word_embeddings=False,
+              max_position_embeddings=512, use_sliding_window=True, sliding_window=45, max_window_layers=1),
 }
 
 

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 # request lengths per configuration: a single token, a page boundary (64, 65), several pages
 LENGTHS = {"A": [40, 33, 64, 100, 65, 37], "B": [33, 64, 47, 130, 38, 90], "C": [35, 129, 64, 80, 200, 41],
-           "D": [300, 34, 129, 64, 260, 161], "E": [400, 140, 33, 151, 290, 64]}
+           "D": [300, 34, 129, 64, 260, 161], "E": [400, 140, 33, 151, 290, 64], "F": [70, 33, 210, 64, 129, 47]}
 TAIL = 32
 
 
@@ -49,7 +49,7 @@ def build_steps(seqs, whole=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_replay_matches_plain_however_the_tokens_are_cut(tmp_path, name, dtype):
     folder = make_folder(tmp_path, name, seed=5)
     cfg, t = plain.read_model(folder)
