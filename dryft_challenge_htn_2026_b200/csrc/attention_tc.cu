@@ -9,17 +9,18 @@
 //
 // A block works on items: 128 consecutive queries of one sequence and one query head. It walks the
 // item's keys in steps of 64 (one cache page).
-//   warp 9, one thread: TMA loads (Q once an item; K and V of each step as [64 keys x 64 columns]
+//   warp 5, one thread: TMA loads (Q once an item; K and V of each step as [64 keys x 64 columns]
 //       boxes, 128-byte swizzle, straight from the page the table names; two stages each), and
 //       the draw of the block's next item from the counter.
-//   warp 8, one thread: all tcgen05.mma:
+//   warp 4, one thread: all tcgen05.mma:
 //       S[128 x 64] = Q.K^T   (both operands from shared memory) into one of two S buffers,
 //       O[128 x HD] += P.V    (P from tensor memory, V from shared memory, N-major).
-//   warps 0-7: softmax, two threads per query row (32 key columns each): they read their part of
-//       the row of S from tensor memory (tcgen05.ld) into registers, agree on the running maximum
-//       through shared memory, rescale their half of the row of O in tensor memory when the
-//       maximum moved, write P as bfloat16 back into tensor memory over their S buffer
-//       (tcgen05.st), and at the end normalise and store their half of the row of O.
+//   warps 0-3: softmax, one thread per query row: it reads its row of S from tensor memory
+//       (tcgen05.ld) into registers, keeps the running maximum, rescales its row of O in tensor
+//       memory when the maximum moved, writes P as bfloat16 back into tensor memory over its S
+//       buffer (tcgen05.st), and at the end normalises and stores its row of O. (Two threads a
+//       row, which agree on the maximum through shared memory and a barrier of their two warps
+//       every step, were 9 to 10 % slower: 56 vs 51 us at 2,048 tokens, 511 vs 471 us at 8,192.)
 // Tensor memory: S0 | S1 | O = 64 + 64 + 128 columns. While the softmax warps work on S of step j,
 // the mma thread issues S of step j + 1 into the other buffer (as soon as P.V of step j - 1 has
 // consumed the P in it) and then P.V of step j: the softmax warps find the next S waiting, and
@@ -47,12 +48,12 @@ namespace {
 
 constexpr int BM = 128, BN = DK_PAGE;             // queries per block, keys per step (one cache page)
 constexpr int PAGES = BN / DK_PAGE;
-constexpr int TPR = BN / 32;                      // softmax threads per query row: 32 key columns each
-constexpr int SOFT = 128 * TPR;                   // softmax threads; then the mma warp, then the loader warp
+constexpr int CPT = BN;                           // key columns of a step a softmax thread takes: its whole row
+constexpr int SOFT = 128;                         // softmax threads, one a query row; then the mma warp, then the loader warp
 constexpr int THREADS = SOFT + 64;
 constexpr int BLOCKS_PER_SM = BN == 64 ? 2 : 1;
 constexpr int TMEM_ALLOC = 2 * BN + 128 <= 256 ? 256 : 512;   // S0 | S1 | O; allocations are powers of two
-constexpr int OC = HD / TPR < 32 ? HD / TPR : 32; // columns of O a thread handles at a time
+constexpr int OC = 32;                            // columns of O a thread handles at a time
 constexpr int HALVES = HD / 64;                   // 64-column swizzle atoms across the head
 constexpr int Q_BYTES = BM * HD * 2, KV_BYTES = BN * HD * 2;   // Q tile; one stage of K or of V
 constexpr int Q_ATOM_BYTES = BM * 128;            // the 128 query rows of one 64-column atom
@@ -153,18 +154,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr));
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-// OC columns of a row of O (OC = 16 or 32)
-template <int N> __device__ __forceinline__ void tmem_ld_o(uint32_t taddr, uint32_t (&r)[N]) {
-    if constexpr (N == 32) tmem_ld32(taddr, r);
-    else tmem_ld16(taddr, r);
-}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile(
@@ -175,13 +164,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
         "r"(r[31])
         : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
-                     taddr),
-                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-                 "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-                 : "memory");
 }
 // 2^x, one MUFU instruction (-inf gives 0)
 __device__ __forceinline__ float ex2(float x) {
@@ -195,21 +177,16 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-template <int N> __device__ __forceinline__ void tmem_st_o(uint32_t taddr, const uint32_t (&r)[N]) {
-    if constexpr (N == 32) tmem_st32(taddr, r);
-    else tmem_st16(taddr, r);
-}
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// grid min(items, 2 * SMs), 320 threads; item = tile * nh + head. tiles[2i] = sequence,
+// grid min(items, 2 * SMs), 192 threads; item = tile * nh + head. tiles[2i] = sequence,
 // tiles[2i+1] = first query (of 128) within the sequence's chunk. q / out [T, nh*HD]; map_q over q
 // as [T, nh*HD]; map_k / map_v over one layer's K / V store as [pages * nkv * 64, HD].
 // sched[0]: next item, sched[1]: blocks that are done; both zero before the launch and after it.
-// Threads 0..255: softmax, two threads per query row (thread t and t+128 share row t & 127 and
-// take 64 of the 128 key columns each; warp w may read the tensor-memory lanes 32 (w % 4)..+31).
-// Warp 8, one thread: every tcgen05.mma. Warp 9, one thread: every TMA load.
+// Threads 0..127: softmax, thread t has query row t (warp w may read the tensor-memory lanes
+// 32 w .. 32 w + 31). Warp 4, one thread: every tcgen05.mma. Warp 5, one thread: every TMA load.
 // The per-step barriers (K, V, S, P, O) complete once a step and bar_q once an item: their phases
 // run on over the items (step, items count what this block has done so far).
 __global__ void __launch_bounds__(THREADS, BLOCKS_PER_SM)
@@ -226,7 +203,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     // [1] a wait ran out; [2], [3]: the block's items, the k-th in slot 2 + (k & 1), written by the loader thread
     volatile int* item_slot = reinterpret_cast<volatile int*>(bars + 12);
-    float* xch = reinterpret_cast<float*>(bars + 14);       // [2][SOFT] row maxima / sums exchanged between the threads of a row
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     pdl_wait();
@@ -367,32 +343,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             if (!ok) atomicExch(err, 1), item_slot[1] = 1;
         }
-    } else {  // ------------------------------------------------------------------ softmax, TPR threads a row
-        const int r = threadIdx.x & 127, part = threadIdx.x >> 7;   // row within the tile = tensor-memory lane; which 32 key columns
+    } else {  // ------------------------------------------------------------------ softmax, a thread a row
+        const int r = threadIdx.x;                           // row within the tile = tensor-memory lane
         const bool valid = r < rows_here;
         const int qpos = pos0 + q0 + r;
         const int key_lo = window > 0 ? max(0, qpos - window + 1) : 0;
         const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
-        const int col0 = part * 32;                          // this thread's key columns within a step
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         for (int i = 0; i < n_blk && ok; i++) {
             const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
-            const int key0 = (blk_lo + i) * BN + col0;
+            const int key0 = (blk_lo + i) * BN;
             if (!mbar_wait(bar_s + b, ph)) { ok = false; break; }
             fence_after();
-            uint32_t v[32];
-            tmem_ld32(t_s + lane_off + b * BN + col0, v);
+            uint32_t v[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; c += 32) tmem_ld32(t_s + lane_off + b * BN + c, *reinterpret_cast<uint32_t(*)[32]>(v + c));
             tmem_wait_ld();
             // every key of the step visible to every row of the tile: no per-element test
             const bool open = window <= 0 && (blk_lo + i) * BN + BN - 1 <= min_pos;
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (open) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                for (int j = 0; j < CPT; j += 2) mx4[(j >> 1) & 3] = max3(mx4[(j >> 1) & 3], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
             } else {
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
+                for (int j = 0; j < CPT; j++) {
                     const int key = key0 + j;
                     const float sc = (valid && key <= qpos && key >= key_lo) ? __uint_as_float(v[j]) : -INFINITY;
                     v[j] = __float_as_uint(sc);
@@ -400,13 +376,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;   // sl2 > 0: scaling keeps the order
-            // the row's maximum is over both threads of the row; once both have been here, both have read their S
-            // (P of one goes over columns of S that the other reads)
-            xch[(i & 1) * SOFT + threadIdx.x] = mx;
-            asm volatile("bar.sync %0, %1;" ::"r"(1 + ((threadIdx.x >> 5) & 3)), "n"(32 * TPR) : "memory");   // the warps that share these rows
             float m_new = fmaxf(m, mx);
-#pragma unroll
-            for (int o = 1; o < TPR; o++) m_new = fmaxf(m_new, xch[(i & 1) * SOFT + ((threadIdx.x + 128 * o) & (SOFT - 1))]);
             // a maximum that moved by less than 8 (a factor 256) keeps the old reference: P stays well inside
             // float32 / bfloat16 range, the final O / l is the same, and O need not be rescaled
             if (m != -INFINITY && m_new - m < 8.f) m_new = m;
@@ -418,26 +388,26 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!mbar_wait(bar_o + (b ^ 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
                 fence_after();
 #pragma unroll 1
-                for (int c = part * (HD / TPR); c < (part + 1) * (HD / TPR); c += OC) {
+                for (int c = 0; c < HD; c += OC) {
                     uint32_t o[OC];
-                    tmem_ld_o(t_o + lane_off + c, o);
+                    tmem_ld32(t_o + lane_off + c, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < OC; j++) o[j] = __float_as_uint(__uint_as_float(o[j]) * alpha);
-                    tmem_st_o(t_o + lane_off + c, o);
+                    tmem_st32(t_o + lane_off + c, o);
                 }
             }
             // P = exp2(S * sl2 - m), its sum, and P as bfloat16 over the first columns of this S buffer
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            uint32_t p[16];
+            uint32_t p[CPT / 2];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
+            for (int j = 0; j < CPT; j += 2) {
                 const float e0 = ex2(fmaf(__uint_as_float(v[j]), sl2, -ms)), e1 = ex2(fmaf(__uint_as_float(v[j + 1]), sl2, -ms));
                 sum4[(j >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 pk = __floats2bfloat162_rn(e0, e1);
                 p[j / 2] = *reinterpret_cast<uint32_t*>(&pk);
             }
-            tmem_st16(t_s + lane_off + b * BN + col0 / 2, p);
+            tmem_st32(t_s + lane_off + b * BN, p);
             l = l * alpha + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m = m_new;
             tmem_wait_st();
@@ -445,19 +415,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_arrive(bar_p + b);
         }
         if (ok) ok = mbar_wait(bar_o + ((step + n_blk - 1) & 1), ((step + n_blk - 1) >> 1) & 1);
-        // the row's sum is over both threads of the row
-        xch[threadIdx.x] = l;
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + ((threadIdx.x >> 5) & 3)), "n"(32 * TPR) : "memory");   // the warps that share these rows
-#pragma unroll
-        for (int o = 1; o < TPR; o++) l += xch[(threadIdx.x + 128 * o) & (SOFT - 1)];
         if (ok) {
             fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = out + ((size_t)(flat0 + r) * nh + h) * HD;
 #pragma unroll 1
-            for (int c = part * (HD / TPR); c < (part + 1) * (HD / TPR); c += OC) {
+            for (int c = 0; c < HD; c += OC) {
                 uint32_t o[OC];
-                tmem_ld_o(t_o + lane_off + c, o);
+                tmem_ld32(t_o + lane_off + c, o);
                 tmem_wait_ld();
                 if (valid) {
 #pragma unroll
@@ -531,7 +496,7 @@ DK_EXPORT int dk_attn_prefill_tc(const void* q, void* out, const void* k_store, 
                                  const int* page_table, int pt_stride, int nh, int nkv, int window, float scale, int* err,
                                  int* sched, cudaStream_t st) {
     if (nh % nkv != 0 || err == nullptr || sched == nullptr || pt_stride < 1) return (int)cudaErrorInvalidValue;
-    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t) + 2 * SOFT * sizeof(float);
+    constexpr size_t smem = 1024 + Q_BYTES + 4 * KV_BYTES + 14 * sizeof(uint64_t);
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
