@@ -357,17 +357,18 @@ def stream_plan(M, N, K, mode, allow_partial=False):
     the shape. Four warps and two persistent blocks per SM while the rows of x leave room for two
     blocks; for a longer K eight warps and one block per SM (as many bytes in flight); beyond that
     K is cut into slices, which needs a caller that takes partial sums (never the SiLU epilogue).
-    With partial sums allowed K is cut further while there are fewer than two tiles per block (more
-    slices cost the consumer more partial sums to add)."""
+    With partial sums allowed K is cut so that the blocks fill the SMs' shared memory with their
+    rings, and further while there are fewer than two tiles per block (more slices cost the
+    consumer more partial sums to add)."""
     sms = sm_count()
 
-    def shape(sk):
+    def shape(sk):                            # (warps, blocks, whether the SMs' shared memory is full of rings)
         if _stream_smem(M, K, sk, 4) <= _STREAM_SMEM_PAIR:
-            return 4, 2 * sms
+            return 4, 2 * sms, True
         if _stream_smem(M, K, sk, 8) <= _STREAM_SMEM_BLOCK:
-            return 8, sms
+            return 8, sms, True
         if _stream_smem(M, K, sk, 4) <= _STREAM_SMEM_BLOCK:
-            return 4, sms
+            return 4, sms, False              # one block of four warps an SM: half the bytes in flight
         return None
 
     sk = 1
@@ -375,14 +376,19 @@ def stream_plan(M, N, K, mode, allow_partial=False):
         sk *= 2
         if sk > 64:
             return None
-    if sk > 1 and (mode == MODE_SILU or not allow_partial):
+    can_slice = allow_partial and mode != MODE_SILU
+    if sk > 1 and not can_slice:
         return None
-    warps, blocks = shape(sk)
-    if allow_partial and mode != MODE_SILU:
+    if can_slice:
+        # two blocks of four warps an SM where up to four slices allow it (what the kernel was tuned on);
+        # else the fewest slices that fill the SMs' shared memory at all, rather than half-empty SMs
+        pair = next((k for k in (1, 2, 4) if k >= sk and shape(k)[:2] == (4, 2 * sms)), None)
+        full = next((k for k in (1, 2, 4, 8) if k >= sk and shape(k)[2]), None)
+        sk = pair or full or sk
         tiles = (N + 15) // 16
-        while sk < 8 and tiles * sk < 2 * blocks and K // (sk * 2) >= 512:
+        while sk < 8 and tiles * sk < 2 * shape(sk)[1] and K // (sk * 2) >= 512 and shape(sk * 2)[2]:
             sk *= 2
-        warps, blocks = shape(sk)
+    warps, blocks, _ = shape(sk)
     return sk, blocks, warps
 
 
