@@ -525,6 +525,23 @@ def skinny_tc_plan(M, N, K, mode, allow_partial=False):
     return best[1]
 
 
+def gated_tc_plan(M, N):
+    """Weight rows per tile for the gated product of a prefill step (gemm_tc, MODE_SILU; N outputs):
+    the height whose tiles leave the last wave of blocks least empty, weighted by what a smaller
+    tile costs (its x tile is re-read for fewer outputs). At 2,048 rows and more every height fills
+    its waves and the largest wins; at 512 rows of the benchmark model 256-row tiles fill 2.05 waves
+    (a third wave for 8 tiles), 192-row tiles 2.76."""
+    sms = sm_count()
+    m_tiles = (M + 127) // 128
+    best = None
+    for bn, worth in ((256, 1.0), (192, 0.95), (160, 0.9), (144, 0.88), (128, 0.85)):
+        tiles = m_tiles * ((N + bn // 2 - 1) // (bn // 2))
+        score = worth * tiles / (-(-tiles // sms) * sms)
+        if best is None or score > best[0] + 1e-9:
+            best = (score, bn)
+    return best[1], 1
+
+
 def gemm_tc_fills_gpu(M, N, min_fill=0.8):
     """Whether gemm_tc's 128 x 256 output tiles, one persistent block per SM, keep the last wave
     at least ``min_fill`` full on average; below that the library's smaller tiles win."""

@@ -34,6 +34,8 @@ def linear(x, w, mode=STORE, allow_partial=False):
         return api.gemm_tc(x, w, mode, None, api.skinny_tc_plan(M, N, K, mode, allow_partial))
     if mode == STORE_F32:
         return torch.mm(x, w.t(), out_dtype=torch.float32)
-    if mode == SILU or api.gemm_tc_fills_gpu(M, N):
-        return api.gemm_tc(x, w, mode)          # TMA + tcgen05, SiLU*up fused into the epilogue
+    if mode == SILU:
+        return api.gemm_tc(x, w, mode, None, api.gated_tc_plan(M, N))   # TMA + tcgen05, SiLU*up fused into the epilogue
+    if api.gemm_tc_fills_gpu(M, N):
+        return api.gemm_tc(x, w, mode)
     return torch.mm(x, w.t())

@@ -409,6 +409,8 @@ def test_gemm_tc(M, N, K):
     close(api.gemm_tc(x, w[:N].contiguous()), ref[:, :N], torch.bfloat16, "gemm_tc")
     g, u = ref[:, :N], ref[:, N:]
     close(api.gemm_tc(x, w, api.MODE_SILU), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gemm_tc silu")
+    for bn in (128, 144, 160, 192):                                   # the tile heights the planner picks for short prefill steps
+        close(api.gemm_tc(x, w, api.MODE_SILU, None, (bn, 1)), g / (1 + torch.exp(-g)) * u, torch.bfloat16, f"gemm_tc silu, {bn} rows a tile")
     api.gemm_tc_check()
     with pytest.raises(api.KernelError):
         api.gemm_tc(rnd(70, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16))
