@@ -206,8 +206,8 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
 // together with them, so up to 16 parts cost one trip to memory after the wait.
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int parts, int n_heads) {
+    pdl_launch_dependents();   // before the wait: see pdl_launch_dependents
     pdl_wait();
-    pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
     const size_t head = (size_t)blockIdx.x * 4 + (threadIdx.x >> 5);
     if (head >= (size_t)n_heads) return;

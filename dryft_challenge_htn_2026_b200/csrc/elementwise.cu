@@ -15,8 +15,8 @@ __global__ void embed_rmsnorm_kernel(const int* tok, const T* __restrict__ embed
                                      const float* __restrict__ w, float eps, int H, int V,
                                      float* h, T* a) {
     __shared__ float red[33];
+    pdl_launch_dependents();   // before the wait: see pdl_launch_dependents
     pdl_wait();
-    pdl_launch_dependents();
     const size_t row = blockIdx.x;
     int t = tok[row];
     t = t < 0 ? 0 : (t >= V ? V - 1 : t);  // ids are validated on the host; never read out of bounds
@@ -104,8 +104,8 @@ __global__ void add_rmsnorm_quad_kernel(float* h, const T* delta, const float* p
         const int c = (threadIdx.x + q * blockDim.x) * 4;
         w4[q] = c < H ? ld4(w + c) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+    pdl_launch_dependents();   // before the wait: see pdl_launch_dependents
     pdl_wait();
-    pdl_launch_dependents();
     float4 v[QPT];
     float ss = 0.f;
 #pragma unroll

@@ -13,9 +13,9 @@
 //   warp 0   producer: one thread issues TMA tile loads (cp.async.bulk.tensor.2d, 128-byte
 //            swizzle) of x [128 x 64] and W [BN x 64] into a shared-memory ring of 4 stages (up
 //            to 12 when few rows of x are loaded); an mbarrier per stage counts the bytes.
-//   warp 1   allocates BN columns of tensor memory; one thread issues tcgen05.mma
-//            (cta_group::1, kind::f16, M = 128, N = BN, K = 16, four per stage) from shared-memory
-//            matrix descriptors, and tcgen05.commit hands each stage back / signals the epilogue.
+//   warp 1   allocates tensor memory; one thread issues tcgen05.mma (cta_group::1, kind::f16,
+//            M = 128, N = BN, K = 16, four per stage) from shared-memory matrix descriptors, and
+//            tcgen05.commit hands each stage back / signals the epilogue.
 //   warps 2-5 epilogue: tcgen05.ld of the accumulator (32 lanes x 32 columns a warp at a time),
 //            conversion, SiLU*up in mode 2, bfloat16 stores.
 // Rows of x beyond M, rows of W beyond N and columns beyond K are zero-filled by TMA; stores are
@@ -25,8 +25,14 @@
 // The same kernel serves decode steps of 17 to 128 rows, where the weights are the traffic and a
 // few tiles cannot fill the GPU: K is cut into SK slices, a unit of work is (tile, slice), and the
 // float32 partial sums of a unit go to ws [SK][M][N] for the consumer to add up (mode 0). There
-// the producer requests the weight tiles of its first stages before it waits for the previous
-// kernel (weights never depend on it) and the rows of x after.
+// the producer requests the weight tiles of its first stages as the very first thing a block does,
+// before the tensor memory is allocated and before the wait for the previous kernel (weights never
+// depend on it), and the rows of x after the wait. A block with a single unit (every decode step
+// the planner sizes) takes one accumulator, and its epilogue goes through the shared memory of the
+// ring, which is free by then: the warps that own the tensor-memory lanes of existing rows copy
+// the raw sums there, then all four warps work out SiLU*up and store whole rows side by side. (A
+// lane storing its own row from registers wrote 32 half-used sectors an instruction, and one or two
+// warps did all the arithmetic: 2 us and 4 us of a 10 and 23 us product at 64 rows.)
 #include <cuda.h>
 
 #include "common.cuh"
@@ -34,7 +40,6 @@
 namespace {
 
 constexpr int BM = 128, BK = 64;
-constexpr int A_BYTES = BM * BK * 2;     // what the mma reads of x per stage: 128 rows of 128 bytes
 constexpr int MAX_STAGES = 12;
 #ifndef DK_WAIT_CYCLES
 #define DK_WAIT_CYCLES 2000000000LL               // about a second: a wait this long has failed
@@ -96,6 +101,16 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -237,24 +252,26 @@ __device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& qe, uint32_t
 // run together share a panel of W). Two accumulators of BN columns alternate in tensor memory: the
 // mma of a tile runs while the epilogue warps drain the tile before it.
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, bf16* out, int M,
                int N, int K, int m_tiles, int tiles, int* err, int SK, float* ws, int STAGES, int a_bytes,
                const __grid_constant__ QkvEpilogue qe) {
     constexpr int B_BYTES = BN * BK * 2;
-    // Shared memory: STAGES weight tiles, then STAGES tiles of x a_bytes apart, then the barriers.
+    // Shared memory: STAGES tiles of x a_bytes apart, then STAGES weight tiles, then the barriers.
     // a_bytes = rows of x that are really loaded x 128 bytes. The mma always reads 128 rows (A_BYTES)
-    // from a tile's start: with fewer loaded rows (a decode step) it reads on into the next tiles or
-    // the padding behind the last one. Those rows of the accumulator are garbage and never stored;
+    // from a tile's start: with fewer loaded rows (a decode step) it reads on into the next tiles of
+    // x or the weight tiles behind them. Those rows of the accumulator are garbage and never stored;
     // what they cost is nothing, what they save is shared memory for more weight tiles in flight.
-    constexpr int TMEM_COLS = 2 * BN <= 256 ? 256 : 512;   // two accumulators; allocations are powers of two
+    constexpr int TMEM_TWO = 2 * BN <= 256 ? 256 : 512;   // two accumulators; allocations are powers of two
+    constexpr int TMEM_ONE = BN <= 128 ? 128 : 256;       // one, where a block has a single unit of work
     constexpr int OUT_COLS = MODE == 2 ? BN / 2 : BN;   // outputs per tile
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024 - (smem_u32(smem_raw) & 1023)) & 1023);   // the swizzle pattern repeats every 1024 bytes
-    uint8_t* smem_a = smem + STAGES * B_BYTES;
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * a_bytes;
     const uint32_t stage_tx = (uint32_t)(B_BYTES + a_bytes);
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem_a + (STAGES - 1) * a_bytes + A_BYTES);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_b + STAGES * B_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;     // [2] mma -> epilogue
     uint64_t* acc_empty = acc_full + 2;      // [2] epilogue -> mma
@@ -264,9 +281,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int k_per = (k_blocks + SK - 1) / SK;   // k blocks per slice; unit u = (tile u / SK, slice u % SK)
     const int units = tiles * SK;
     const bool early_w = SK > 1 || ws != nullptr || m_tiles == 1;   // decode: weights before the wait
+    const bool single = units <= (int)gridDim.x;  // a block has one unit of work
+    const uint32_t tmem_cols = single ? TMEM_ONE : TMEM_TWO;
+    // whether that unit's tile fits the ring's shared memory as float32 rows (see the epilogue)
+    const bool staged = single && STAGES * (B_BYTES + a_bytes) >= BM * (BN + 4) * 4;
+    int early = 0;                                // stages whose weight tiles thread 0 requests before the block is set up
 
     if (!early_w) pdl_wait();
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_x) : "memory");
         for (int s = 0; s < STAGES; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
@@ -277,9 +301,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // Decode: the weight tiles of the first unit's first stages are requested here, before the
+        // tensor memory is there (its allocation waits while a block of the kernel before, still
+        // running on this SM, holds its columns) and long before the rows of x may be read.
+        if (early_w && !DK_STALLED) {
+            const int unit = blockIdx.x, tile = unit / SK, slice = unit % SK;
+            const int n0 = (tile / m_tiles) * OUT_COLS;
+            const int kb0 = slice * k_per, kb1 = min(k_blocks, kb0 + k_per);
+            for (int kb = kb0; kb < kb1 && early < STAGES; kb++, early++) {
+                uint8_t* stage = smem_b + early * B_BYTES;
+                mbar_expect_tx(&full[early], stage_tx);
+                if (MODE == 2) {
+                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early]);
+                    tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[early]);
+                } else {
+                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early]);
+                }
+            }
+        }
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -312,14 +354,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         unit = units;
                         break;
                     }
-                    uint8_t* stage = smem + s * B_BYTES;
-                    mbar_expect_tx(&full[s], stage_tx);
+                    uint8_t* stage = smem_b + s * B_BYTES;
+                    if (it >= early) mbar_expect_tx(&full[s], stage_tx);
                     if (waited) {
                         tma_load_2d(smem_a + s * a_bytes, &map_x, kb * BK, m0, &full[s]);
                     } else {
                         early_kb[it] = kb;
                         early_m0[it] = m0;
                     }
+                    if (it < early) continue;
                     if (MODE == 2) {
                         tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
                         tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
@@ -353,7 +396,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         break;
                     }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_addr = smem_u32(smem_a + s * a_bytes), b_addr = smem_u32(smem + s * B_BYTES);
+                    const uint32_t a_addr = smem_u32(smem_a + s * a_bytes), b_addr = smem_u32(smem_b + s * B_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++)
                         umma_f16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), IDESC, (kb > kb0) | (k != 0));
@@ -371,12 +414,79 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const int buf = iter & 1;
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * OUT_COLS;
             const int row = m0 + q * 32 + lane;
-            if (!mbar_wait(&acc_full[buf], (iter >> 1) & 1)) {
+            const bool arrived = mbar_wait(&acc_full[buf], (iter >> 1) & 1);
+            if (!arrived) {
                 atomicExch(err, 3);
-                break;
+                if (!staged) break;
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = tmem + buf * BN + ((uint32_t)(q * 32) << 16);
+            if (MODE < 3 && staged) {
+                // A decode step: the block's one tile goes through shared memory (the ring is done with: every
+                // stage has been read by the mma that filled this accumulator), so that a row leaves as whole
+                // 16-byte pieces side by side. Straight from the registers every lane would store to a row of
+                // its own: 32 separate half-used sectors an instruction, 2 us for a tile of 64 x 128 partial sums.
+                // In mode 2 the raw gate and up sums are staged side by side and SiLU * up is worked out on the way
+                // out, by all four warps: the tensor-memory lanes of the rows that exist belong to one or two.
+                constexpr int W = MODE == 2 ? 2 * OUT_COLS : OUT_COLS;   // staged floats a row
+                constexpr int LD = W + 4;                                // LD / 4 is odd: no bank conflicts
+                float* stg = reinterpret_cast<float*>(smem);
+                if (arrived && q * 32 < M - m0) {
+                    float* dst = stg + (q * 32 + lane) * LD;
+#pragma unroll 1
+                    for (int c = 0; c < W; c += 64) {
+                        uint32_t v[32], u[32];
+                        tmem_ld32_nowait(acc + c, v);
+                        if (c + 32 < W) tmem_ld32_nowait(acc + c + 32, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            if (c + i < W) *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            if (c + 32 + i < W) *reinterpret_cast<uint4*>(dst + c + 32 + i) = make_uint4(u[i], u[i + 1], u[i + 2], u[i + 3]);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+                const int rows_here = min(M - m0, BM);
+                const int t = (warp - 2) * 32 + lane;
+                if (arrived) {
+                    for (int idx = t; idx < rows_here * (OUT_COLS / 4); idx += 128) {
+                        const int r = idx / (OUT_COLS / 4), c = (idx % (OUT_COLS / 4)) * 4;
+                        float4 f = *reinterpret_cast<const float4*>(stg + r * LD + c);
+                        if (MODE == 2) {
+                            const float4 up = *reinterpret_cast<const float4*>(stg + r * LD + OUT_COLS + c);
+                            f.x = __fdividef(f.x, 1.f + __expf(-f.x)) * up.x;   // 2 ulp: far below the bf16 rounding that follows
+                            f.y = __fdividef(f.y, 1.f + __expf(-f.y)) * up.y;
+                            f.z = __fdividef(f.z, 1.f + __expf(-f.z)) * up.z;
+                            f.w = __fdividef(f.w, 1.f + __expf(-f.w)) * up.w;
+                        }
+                        const int col = n0 + c;
+                        if (col >= N) continue;
+                        if (ws != nullptr) {
+                            float* dst = ws + ((size_t)slice * M + m0 + r) * N + col;
+                            if (N % 4 == 0) {
+                                *reinterpret_cast<float4*>(dst) = f;
+                            } else {
+                                const float e[4] = {f.x, f.y, f.z, f.w};
+                                for (int i = 0; i < 4 && col + i < N; i++) dst[i] = e[i];
+                            }
+                        } else {
+                            bf16* dst = out + (size_t)(m0 + r) * N + col;
+                            if (N % 4 == 0) {
+                                uint2 pk;
+                                *reinterpret_cast<__nv_bfloat162*>(&pk.x) = __floats2bfloat162_rn(f.x, f.y);
+                                *reinterpret_cast<__nv_bfloat162*>(&pk.y) = __floats2bfloat162_rn(f.z, f.w);
+                                *reinterpret_cast<uint2*>(dst) = pk;
+                            } else {
+                                const float e[4] = {f.x, f.y, f.z, f.w};
+                                for (int i = 0; i < 4 && col + i < N; i++) dst[i] = __float2bfloat16_rn(e[i]);
+                            }
+                        }
+                    }
+                }
+                break;                                              // the block's only unit
+            }
             if (MODE == 3) qkv_epilogue_row<BN, 128>(qe, acc, row, M, n0, N);
             if (MODE == 4) qkv_epilogue_row<BN, 64>(qe, acc, row, M, n0, N);
 #pragma unroll 1
@@ -436,7 +546,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (!early_w) pdl_launch_dependents();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols) : "memory");
     }
 }
 
@@ -479,10 +589,16 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
     // the next of 16, 32, 64 that holds them, which leaves shared memory for more weight tiles in flight
     const int a_rows = M > 64 ? 128 : M > 32 ? 64 : M > 16 ? 32 : 16;
     const int a_bytes = a_rows * BK * 2;
-    int stages = (200 * 1024 - (A_BYTES - a_bytes)) / (B_BYTES + a_bytes);
+    const int m_tiles = (M + BM - 1) / BM, tiles = m_tiles * ((N + OUT_COLS - 1) / OUT_COLS);
+    const int units = tiles * SK;
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    constexpr size_t TAIL = (2 * MAX_STAGES + 4) * sizeof(uint64_t) + 16;
+    const size_t budget = 200 * 1024;
+    int stages = (int)(budget / (B_BYTES + a_bytes));
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    const size_t smem = 1024 + (size_t)stages * B_BYTES + (size_t)(stages - 1) * a_bytes + A_BYTES +
-                        (2 * MAX_STAGES + 4) * sizeof(uint64_t) + 16;
+    const size_t smem = 1024 + (size_t)stages * (B_BYTES + a_bytes) + TAIL;
     static size_t attr = 0;
     if (smem > attr) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -494,11 +610,6 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
     if (e) return e;
     e = make_map(&mw, W, MODE == 2 ? 2LL * N : N, K, MODE == 2 ? BN / 2 : BN);
     if (e) return e;
-    const int m_tiles = (M + BM - 1) / BM, tiles = m_tiles * ((N + OUT_COLS - 1) / OUT_COLS);
-    const int units = tiles * SK;
-    int sms = 0, dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return dk_launch(gemm_tc_kernel<BN, MODE>, dim3(units < sms ? units : sms), dim3(192), smem, st, mx, mw, out, M, N, K,
                      m_tiles, tiles, err, SK, ws, stages, a_bytes, qe);
 }
