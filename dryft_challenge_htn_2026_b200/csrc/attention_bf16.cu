@@ -132,13 +132,14 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
     const int t_lo = key_lo / DK_PAGE, t_hi = pos / DK_PAGE;
     const int per = (t_hi - t_lo + 1 + nsplit - 1) / nsplit;
     const int jt0 = t_lo + split * per, jt1 = pos >= 0 ? min(t_hi + 1, jt0 + per) : jt0;  // [jt0, jt1)
+    const uint64_t stream_once = l2_evict_first();
     auto fetch = [&](int jt, int slot) {
         const size_t off = kv_offset(pt[jt], nkv, kvh, warp * 16, HD);
         bf16* dst = ring + slot * CHUNK;
         for (int c = lane; c < 16 * CPR; c += 32) {
             const int row = c / CPR, col = (c % CPR) * 8;
-            cp_async16(dst + row * KSTR + col, k_store + off + (size_t)row * HD + col);
-            cp_async16(dst + 16 * KSTR + row * KSTR + col, v_store + off + (size_t)row * HD + col);
+            cp_async16(dst + row * KSTR + col, k_store + off + (size_t)row * HD + col, stream_once);
+            cp_async16(dst + 16 * KSTR + row * KSTR + col, v_store + off + (size_t)row * HD + col, stream_once);
         }
     };
     int issued = 0;                           // chunks requested so far; chunk i is commit group i

@@ -33,6 +33,11 @@ __device__ __forceinline__ void cp_async16(bf16* smem, const bf16* gmem) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(a), "l"(gmem) : "memory");
 }
+// the same with a cache policy (see l2_evict_first): a decode step reads a sequence's keys and values once
+__device__ __forceinline__ void cp_async16(bf16* smem, const bf16* gmem, uint64_t policy) {
+    uint32_t a = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(a), "l"(gmem), "l"(policy) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");

@@ -65,6 +65,15 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 // weights only.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
+// Cache policy for what a decode step reads exactly once (weights, the keys and values of a sequence):
+// first in line to leave the L2, so that gigabytes of them streaming through do not push out the few
+// megabytes that the kernels of a step hand to one another (the residual stream, partial sums, q).
+__device__ __forceinline__ uint64_t l2_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
 static int g_pdl = 0;
 DK_EXPORT void dk_set_pdl(int on) { g_pdl = on; }
 

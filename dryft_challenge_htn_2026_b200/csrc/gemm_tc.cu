@@ -87,6 +87,14 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
                  "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
                  : "memory");
 }
+// the same with a cache policy (see l2_evict_first): the weight tiles of a decode step, read once
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
+            smem_u32(dst)),
+        "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
 // groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -305,6 +313,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         // tensor memory is there (its allocation waits while a block of the kernel before, still
         // running on this SM, holds its columns) and long before the rows of x may be read.
         if (early_w && !DK_STALLED) {
+            const uint64_t stream_once = l2_evict_first();
             const int unit = blockIdx.x, tile = unit / SK, slice = unit % SK;
             const int n0 = (tile / m_tiles) * OUT_COLS;
             const int kb0 = slice * k_per, kb1 = min(k_blocks, kb0 + k_per);
@@ -312,10 +321,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 uint8_t* stage = smem_b + early * B_BYTES;
                 mbar_expect_tx(&full[early], stage_tx);
                 if (MODE == 2) {
-                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early]);
-                    tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[early]);
+                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early], stream_once);
+                    tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[early], stream_once);
                 } else {
-                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early]);
+                    tma_load_2d(stage, &map_w, kb * BK, n0, &full[early], stream_once);
                 }
             }
         }
@@ -332,6 +341,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0 && !DK_STALLED) {  // ---------------------------------------------- producer
+            const uint64_t stream_once = l2_evict_first();
             int it = 0;   // stages issued so far, over all units of this block
             int s = 0;    // it % STAGES, and round = (it / STAGES) & 1, kept by counting (no division on this path)
             uint32_t round = 0;
@@ -363,7 +373,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         early_m0[it] = m0;
                     }
                     if (it < early) continue;
-                    if (MODE == 2) {
+                    if (early_w) {            // a decode step reads a weight tile once
+                        if (MODE == 2) {
+                            tma_load_2d(stage, &map_w, kb * BK, n0, &full[s], stream_once);
+                            tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s], stream_once);
+                        } else {
+                            tma_load_2d(stage, &map_w, kb * BK, n0, &full[s], stream_once);
+                        }
+                    } else if (MODE == 2) {
                         tma_load_2d(stage, &map_w, kb * BK, n0, &full[s]);
                         tma_load_2d(stage + B_BYTES / 2, &map_w, kb * BK, N + n0, &full[s]);
                     } else {

@@ -44,8 +44,8 @@ constexpr int SMEM_LIMIT = 227 * 1024;        // dynamic shared memory a block m
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // 16-byte asynchronous copy global -> shared, not kept in L1; `real` false writes zeros instead.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool real) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(real ? 16 : 0) : "memory");
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool real, uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(real ? 16 : 0), "l"(policy) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -106,6 +106,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
     const int my_tiles = tile0 < tiles ? (tiles - tile0 + tile_step - 1) / tile_step : 0;
     const int total = my_tiles * n_stages;    // stages of this block; stage i: tile i / n_stages, piece i % n_stages
 
+    const uint64_t stream_once = l2_evict_first();   // a weight is read once a step
     auto fetch = [&](int i, int slot) {       // weight rows of block stage i into this warp's ring slot
         const int tile = tile0 + (i / n_stages) * tile_step;
         const int kk = (i % n_stages) * STAGE_K;
@@ -116,7 +117,7 @@ gemv_stream_kernel(const bf16* x, const bf16* __restrict__ W, void* out, float* 
         for (int r = 0; r < WR; r++) {
             const int n = tile * OUTS + (r % OUTS);
             const size_t row = (size_t)min(n, N - 1) + (r >= OUTS ? (size_t)N : 0);
-            cp_async16(stage + r * ROW_STRIDE, W + row * K + k_begin + kk + lane * 8, n < N);
+            cp_async16(stage + r * ROW_STRIDE, W + row * K + k_begin + kk + lane * 8, n < N, stream_once);
         }
     };
 
