@@ -494,10 +494,13 @@ def test_attention_prefill_tc(nh, nkv, hd, window, before, new):
     assert all(int(c.abs().sum()) == 0 for c in api._attn_sched.values())   # the work counter is left at zero
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 6144, 2560), (33, 2560, 4096), (128, 2560, 9728), (17, 300, 520), (100, 1000, 1288)])
+@pytest.mark.parametrize("M,N,K", [(64, 6144, 2560), (33, 2560, 4096), (128, 2560, 9728), (17, 300, 520), (100, 1000, 1288),
+                                   (40, 1002, 520)])
 def test_gemm_tc_on_a_decode_step_of_17_to_128_rows(M, N, K):
     """One tile of rows, K in slices with float32 partial sums, weights requested before the wait
-    for the previous kernel (programmatic launch on, a kernel in front)."""
+    for the previous kernel (programmatic launch on, a kernel in front); the epilogue through
+    shared memory with whole 16-byte pieces of a row, and element by element where the width is no
+    multiple of four (1,002 outputs, 501 gated ones)."""
     x, w = rnd(M, K, dtype=torch.bfloat16, seed=80), rnd(N, K, dtype=torch.bfloat16, seed=81, scale=K ** -0.5)
     ref = x.float() @ w.float().t()
     api.set_pdl(True)
