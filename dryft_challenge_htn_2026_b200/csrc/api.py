@@ -431,16 +431,15 @@ _tc_err = None
 def gemm_tc(x, w, mode=MODE_STORE, out=None, plan=None):
     """out = x . w^T (mode MODE_STORE, MODE_STORE_F32) or silu(x . gate^T) * (x . up^T) (mode
     MODE_SILU, w = [gate; up]) on tcgen05 tensor cores, TMA-fed, float32 accumulation in tensor
-    memory. ``plan`` = (weight rows per tile: 128 or 256, for MODE_SILU also 144, 160 and 192;
-    slices of K): with more than one slice (mode MODE_STORE) a ``Partial`` comes back instead of a
-    tensor."""
+    memory. ``plan`` = (weight rows per tile, one of TC_TILE_HEIGHTS; slices of K): with more than
+    one slice (mode MODE_STORE) a ``Partial`` comes back instead of a tensor."""
     global _tc_err
     _need(x, "x", torch.bfloat16, 2), _need(w, "w", torch.bfloat16, 2), _need(out, "out", None, 2)
     M, K = x.shape
     N = w.shape[0] // 2 if mode == MODE_SILU else w.shape[0]
     bn, sk = plan or (256, 1)
     if K % 8 or w.shape[1] != K or mode not in (MODE_STORE, MODE_STORE_F32, MODE_SILU) \
-            or bn not in ((128, 144, 160, 192, 256) if mode == MODE_SILU else (128, 256)):
+            or bn not in TC_TILE_HEIGHTS:
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} mode {mode} not supported (K % 8 == 0)")
     kb = (K + 63) // 64
     if sk < 1 or (sk > 1 and (mode != MODE_STORE or (sk - 1) * ((kb + sk - 1) // sk) >= kb)):
@@ -500,29 +499,37 @@ def gemm_tc_qkv(x, w, q_out, q_norm_w, k_norm_w, cos, sin, eps, row_pos, row_seq
 TC_SKINNY_MAX_ROWS = 128
 
 
+TC_TILE_HEIGHTS = (128, 144, 160, 176, 192, 208, 224, 240, 256)   # weight rows a tile of gemm_tc
+
+
 def skinny_tc_plan(M, N, K, mode, allow_partial=False):
-    """(weight rows per tile, slices of K) for gemm_tc on a decode step of up to 128 rows: one
-    block per unit (tile, slice), as many units as fit the SMs, slices of at least 8 blocks of 64
-    columns (fewer cannot keep the load ring busy), fewer slices on a tie."""
+    """(weight rows per tile, slices of K) for gemm_tc on a decode step of up to 128 rows. A unit of
+    work is (tile, slice), with a block of its own while the units fit the SMs; all blocks stream
+    at once, so the step takes as long as its largest unit: tile height x blocks of 64 columns in
+    a slice (x waves, should the tiles alone exceed the SMs). The plan with the smallest such unit
+    wins; among plans within 3 % of it the one with the fewest slices (partial sums are written and
+    added up again), then the larger tile. Slices hold at least 8 blocks of 64 columns (fewer
+    cannot keep the load ring busy). The gated product has no slices (SiLU needs whole sums)."""
     kb = (K + 63) // 64
     sms = sm_count()
-    if mode == MODE_SILU:      # no slices (SiLU needs whole sums): the tile width that covers most SMs
-        def fill(bn):
+    if mode == MODE_SILU:
+        def span(bn):
             tiles = (N + bn // 2 - 1) // (bn // 2)
-            return tiles / (-(-tiles // sms) * sms)
-        return max((256, 192, 160, 144, 128), key=fill), 1
+            return bn * -(-tiles // sms)
+        return min(TC_TILE_HEIGHTS, key=lambda bn: (span(bn), bn)), 1
     if mode != MODE_STORE or not allow_partial:
         return 256, 1
-    best = None
-    for bn in (256, 128):
+    plans = []
+    for bn in TC_TILE_HEIGHTS:
         tiles = (N + bn - 1) // bn
         sk = max(1, min(sms // tiles, kb // 8))
         while sk > 1 and (sk - 1) * ((kb + sk - 1) // sk) >= kb:
             sk -= 1
-        key = (min(tiles * sk, sms), -sk)
-        if best is None or key > best[0]:
-            best = (key, (bn, sk))
-    return best[1]
+        waves = -(-tiles * sk // sms)
+        plans.append((bn * ((kb + sk - 1) // sk) * waves, sk, bn))
+    least = min(p[0] for p in plans)
+    _, sk, bn = min((p for p in plans if p[0] <= 1.03 * least), key=lambda p: (p[1], p[0], -p[2]))
+    return bn, sk
 
 
 def gated_tc_plan(M, N):

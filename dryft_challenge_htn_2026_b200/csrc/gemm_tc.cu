@@ -637,8 +637,8 @@ int launch(const bf16* x, const bf16* W, bf16* out, int M, int N, int K, int* er
 // err: device int, receives a code if a bounded wait ran out. K % 8 == 0; 16-byte aligned x, W.
 // ws != null (mode 0): float32 results into ws [SK][M][N] instead of out, the partial sums of SK
 // slices of K (every slice at least one block of 64 columns; SK = 1: the product itself in
-// float32). bn: weight rows a tile, 128 or 256 (mode 2 also 144, 160, 192: half of them gate rows,
-// half up rows, which lets the tiles of a short step cover more SMs).
+// float32). bn: weight rows a tile, a multiple of 16 from 128 to 256 (mode 2: half of them gate
+// rows, half up rows): the planner picks the height whose tiles and slices load the SMs most evenly.
 DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int mode, int* err, int SK, float* ws,
                          int bn, cudaStream_t st) {
     if (M < 1 || N < 1 || K < 8 || K % 8 != 0 || err == nullptr || SK < 1) return (int)cudaErrorInvalidValue;
@@ -646,13 +646,12 @@ DK_EXPORT int dk_gemm_tc(const void* x, const void* W, void* out, int M, int N, 
     const int k_blocks = (K + 63) / 64, k_per = (k_blocks + SK - 1) / SK;
     if (SK > 1 && (mode != 0 || ws == nullptr || (SK - 1) * k_per >= k_blocks)) return (int)cudaErrorInvalidValue;
     if (ws != nullptr && mode != 0) return (int)cudaErrorInvalidValue;
-    if (mode == 2 && bn == 128) return launch<128, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 2 && bn == 144) return launch<144, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 2 && bn == 160) return launch<160, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 2 && bn == 192) return launch<192, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 2) return launch<256, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 0 && bn == 128) return launch<128, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
-    if (mode == 0) return launch<256, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st);
+#define TILE_HEIGHT(BN)                                                                                          \
+    if (bn == BN && mode == 2) return launch<BN, 2>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st); \
+    if (bn == BN && mode == 0) return launch<BN, 0>((const bf16*)x, (const bf16*)W, (bf16*)out, M, N, K, err, SK, ws, st)
+    TILE_HEIGHT(128); TILE_HEIGHT(144); TILE_HEIGHT(160); TILE_HEIGHT(176); TILE_HEIGHT(192);
+    TILE_HEIGHT(208); TILE_HEIGHT(224); TILE_HEIGHT(240); TILE_HEIGHT(256);
+#undef TILE_HEIGHT
     return (int)cudaErrorInvalidValue;
 }
 

@@ -505,7 +505,8 @@ def test_gemm_tc_on_a_decode_step_of_17_to_128_rows(M, N, K):
     ref = x.float() @ w.float().t()
     api.set_pdl(True)
     try:
-        plans = {api.skinny_tc_plan(M, N, K, api.MODE_STORE, True), (128, 1), (256, 1), (128, 2), (256, 3)}
+        plans = {api.skinny_tc_plan(M, N, K, api.MODE_STORE, True), (128, 1), (256, 1), (128, 2), (256, 3), (144, 2), (176, 1),
+                 (208, 3), (240, 2)}
         for bn, sk in sorted(plans):
             if sk > 1 and (sk - 1) * (((K + 63) // 64 + sk - 1) // sk) >= (K + 63) // 64:
                 continue
@@ -518,7 +519,7 @@ def test_gemm_tc_on_a_decode_step_of_17_to_128_rows(M, N, K):
         close(r, ref, torch.bfloat16, "gemm_tc float32 out")
         if N % 2 == 0:
             g, u = ref.chunk(2, dim=1)
-            for bn in (128, 144, 160, 192, 256):
+            for bn in api.TC_TILE_HEIGHTS:
                 close(api.gemm_tc(x, w, api.MODE_SILU, None, (bn, 1)), g / (1 + torch.exp(-g)) * u, torch.bfloat16,
                       f"gemm_tc silu, few rows, {bn} weight rows a tile")
         api.gemm_tc_check()

@@ -34,13 +34,19 @@ def test_skinny_tc_plan_gives_every_slice_work_and_no_more_units_than_sms():
         for mode, partial in ((api.MODE_STORE, True), (api.MODE_STORE, False), (api.MODE_SILU, False), (api.MODE_STORE_F32, False)):
             bn, sk = api.skinny_tc_plan(M, N, K, mode, partial)
             kb = (K + 63) // 64
-            assert bn in ((128, 144, 160, 192, 256) if mode == api.MODE_SILU else (128, 256))
+            assert bn in api.TC_TILE_HEIGHTS
             assert sk >= 1 and (sk - 1) * ((kb + sk - 1) // sk) < kb          # no slice without a block of K
             assert sk == 1 or (mode == api.MODE_STORE and partial)
             if sk > 1:
                 assert ((N + bn - 1) // bn) * sk <= api.sm_count()
     # the gated product of the benchmark model: the tile width that covers most SMs in one wave
     assert api.skinny_tc_plan(64, 9728, 2560, api.MODE_SILU) == (144, 1)
+    if api.sm_count() == 148:
+        # 12,288 outputs in tiles of 88: 140 blocks; 17,408 in tiles of 120: 146 (256-row tiles would leave 52 and 12 SMs idle)
+        assert api.skinny_tc_plan(64, 12288, 4096, api.MODE_SILU) == (176, 1)
+        assert api.skinny_tc_plan(64, 17408, 5120, api.MODE_SILU) == (240, 1)
+        # 4,096 outputs over 4,096 columns: 29 tiles of 144 rows in 5 slices (145 blocks of 13 blocks of K) beat 32 x 4 of 16
+        assert api.skinny_tc_plan(64, 4096, 4096, api.MODE_STORE, True) == (144, 5)
 
 
 def test_decode_splits_depend_on_the_batch_only_and_stay_within_what_the_merge_takes():
