@@ -318,21 +318,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                                 dkb + (uint64_t)((hh * KV_ATOM_BYTES + k * 32) >> 4), IDESC_S, (hh | k) != 0);
                 umma_commit(bar_s + b);
             };
+            // S runs two steps ahead of P.V: S(0) and S(1) at once, then S(i + 2) right behind P.V(i), whose P it
+            // overwrites. The mma of one thread execute in the order of their issue, so S(i + 2) needs no wait
+            // for P.V(i) to end. (With S one step ahead and that wait, a timeline of the steps showed the
+            // chain P(i-1) -> P.V(i-1) -> its barrier -> S(i+1) -> softmax(i+1) at 1,500 clocks a step where
+            // the exponentials of the SM's two blocks take 1,070 and their mma 1,050.)
             bool ok = mbar_wait(bar_q, items & 1) && mbar_wait(bar_k + (step & 1), (step >> 1) & 1);
             if (ok) {
                 fence_after();
                 issue_s(0);
             }
+            if (ok && n_blk > 1) {
+                ok = mbar_wait(bar_k + ((step + 1) & 1), ((step + 1) >> 1) & 1);
+                if (ok) {
+                    fence_after();
+                    issue_s(1);
+                }
+            }
             for (int i = 0; i < n_blk && ok; i++) {
                 const uint32_t t = step + i, b = t & 1, ph = (t >> 1) & 1;
-                if (i + 1 < n_blk) {                        // S of the next step, while the softmax warps work on this one
-                    const uint32_t tn = t + 1;
-                    if (!mbar_wait(bar_k + (tn & 1), (tn >> 1) & 1)) { ok = false; break; }
-                    // its buffer held P of the step before this one: P.V of that step must be done with it
-                    if (i >= 1 && !mbar_wait(bar_o + (tn & 1), ((t - 1) >> 1) & 1)) { ok = false; break; }
-                    fence_after();
-                    issue_s(i + 1);
-                }
                 if (!mbar_wait(bar_p + b, ph)) { ok = false; break; }
                 if (!mbar_wait(bar_v + b, ph)) { ok = false; break; }   // P is written, V is here
                 fence_after();
@@ -340,6 +344,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int k = 0; k < BN / 16; k++)
                     umma_ts(t_o, t_s + b * BN + k * 8, dv + (uint64_t)((b * KV_BYTES + k * 16 * 128) >> 4), IDESC_PV, (i | k) != 0);   // the item's first product overwrites O
                 umma_commit(bar_o + b);
+                if (i + 2 < n_blk) {                        // S of the step after next, into the buffer whose P was just used
+                    const uint32_t t2 = t + 2;
+                    if (!mbar_wait(bar_k + (t2 & 1), (t2 >> 1) & 1)) { ok = false; break; }
+                    fence_after();
+                    issue_s(i + 2);
+                }
             }
             if (!ok) atomicExch(err, 1), item_slot[1] = 1;
         }
