@@ -21,12 +21,22 @@
 //       buffer (tcgen05.st), and at the end normalises and stores its row of O. (Two threads a
 //       row, which agree on the maximum through shared memory and a barrier of their two warps
 //       every step, were 9 to 10 % slower: 56 vs 51 us at 2,048 tokens, 511 vs 471 us at 8,192.)
-// Tensor memory: S0 | S1 | O = 64 + 64 + 128 columns. While the softmax warps work on S of step j,
-// the mma thread issues S of step j + 1 into the other buffer (as soon as P.V of step j - 1 has
-// consumed the P in it) and then P.V of step j: the softmax warps find the next S waiting, and
-// the two products of a block run under its own softmax. K of step j + 2 is fetched as soon as S
-// of step j has been computed, V as soon as P.V has. Two blocks fit on an SM (96 KB shared, 256
-// columns of tensor memory each).
+// Tensor memory: S0 | S1 | O = 64 + 64 + 128 columns. S runs two steps ahead of P.V: the mma thread
+// issues S of steps 0 and 1 at once, and S of step j + 2 right behind P.V of step j, into the buffer
+// whose P that product has just read (the mma of one thread execute in issue order): the softmax
+// warps always find the next S waiting, and the products of a block run under its own softmax. K
+// of step j + 2 is fetched as soon as S of step j has been computed, V as soon as P.V has. Two
+// blocks fit on an SM (96 KB shared, 256 columns of tensor memory each).
+// What a step costs (a timeline of block clocks, test build): the exponentials of the SM's two
+// blocks, which fall into step with each other, take 1,070 clocks (16 a clock), their mma 1,290 as
+// issued here: S = Q.K^T with 64 keys a step reads 6 KB of shared memory per 128 x 64 x 16 product,
+// 48 clocks at 128 bytes a clock against 33 of arithmetic, so S is bound by shared memory (384
+// clocks a step against 262 for P.V, whose A operand comes from tensor memory). A step of the two
+// blocks takes about 1,480. Q in tensor memory instead (S in the TS form, shared memory for K only)
+// needs 64 more columns, which leaves one S buffer for two blocks an SM: built and measured, 4-7 %
+// slower on the whole prefill (every latency between softmax and mma is then in the open). Two
+// query tiles a block with 128-key steps and all 512 columns is the form that removes both limits;
+// it is not built.
 // The grid is persistent: two blocks an SM, each takes the next (tile, head) from a counter in
 // global memory until none is left. (With a block per tile the SMs did not take a new block while
 // one of their two was still running: the light tiles started only when a whole SM had drained,

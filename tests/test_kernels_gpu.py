@@ -400,11 +400,14 @@ def test_gemv_stream(M, N, K):
         assert api.stream_plan(M, N, 9728, api.MODE_SILU) is None
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (100, 300, 72), (300, 200, 136), (1000, 520, 2560), (65, 2560, 1024)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (100, 300, 72), (300, 200, 136), (1000, 520, 2560), (65, 2560, 1024),
+                                   (1157, 600, 20544)])
 def test_gemm_tc(M, N, K):
     """The TMA + tcgen05 product against x.w^T in float32: full tiles, ragged edges in M, N and K,
-    several tiles per block (persistent loop, both accumulators), plain and SiLU*up epilogues."""
-    x, w = rnd(M, K, dtype=torch.bfloat16, seed=81), rnd(2 * N, K, dtype=torch.bfloat16, seed=82, scale=0.05)
+    several tiles per block (persistent loop, both accumulators), plain and SiLU*up epilogues; and
+    rows of x so long that the row tiles are walked in more than one group (ten row tiles in groups
+    of eight: every tile once, none twice)."""
+    x, w = rnd(M, K, dtype=torch.bfloat16, seed=81), rnd(2 * N, K, dtype=torch.bfloat16, seed=82, scale=0.05 * min(1.0, (2560 / K) ** 0.5))
     ref = x.float() @ w.float().T
     close(api.gemm_tc(x, w[:N].contiguous()), ref[:, :N], torch.bfloat16, "gemm_tc")
     g, u = ref[:, :N], ref[:, N:]
