@@ -35,8 +35,13 @@
 // blocks takes about 1,480. Q in tensor memory instead (S in the TS form, shared memory for K only)
 // needs 64 more columns, which leaves one S buffer for two blocks an SM: built and measured, 4-7 %
 // slower on the whole prefill (every latency between softmax and mma is then in the open). Two
-// query tiles a block with 128-key steps and all 512 columns is the form that removes both limits;
-// it is not built.
+// query tiles a block with 128-key steps and all 512 columns of tensor memory (S_A | S_B | O_A |
+// O_B, one softmax thread a row, the products of one tile issued while the other tile's softmax
+// runs) was built too and gave the same results, but 529 us against 477 at 8,192 tokens (623 with
+// two threads a row): the exponential unit does 16 a clock and SM (measured), 1,024 clocks for a
+// tile's 128 x 128 scores, a tile's two products take 1,050, and with one S buffer a tile the
+// two follow one another: 4,150 clocks for two tiles x 128 keys where the two blocks of this
+// kernel need 2,960 for the same work.
 // The grid is persistent: two blocks an SM, each takes the next (tile, head) from a counter in
 // global memory until none is left. (With a block per tile the SMs did not take a new block while
 // one of their two was still running: the light tiles started only when a whole SM had drained,
