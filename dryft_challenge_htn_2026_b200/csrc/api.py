@@ -255,17 +255,24 @@ def attention_prefill_bf16(q, out, k_store, v_store, tiles, cu_q, seq_pos0, page
                                          int(window or 0), c_float(scale), _stream()), "attention_prefill_bf16")
 
 
-def decode_splits(n_seq, n_kv_heads, group, max_splits=8, resident_blocks=None):
-    """Number of key splits for decode attention, fixed for a batch size (it must not depend on
-    sequence lengths, which change under a captured graph). While all blocks fit the GPU at once
-    (two per SM with the three-deep rings): as many splits as keep it so. Beyond that: enough for
-    about six waves of blocks, which evens out sequences of unequal lengths (measured at batch 64:
-    133 us unsplit, 115 us in four splits)."""
+DECODE_MAX_SPLITS = 32          # the merge kernel takes 4 x 32 parts a head
+
+
+def decode_splits(n_seq, n_kv_heads, group, table_pages=0, max_splits=8, resident_blocks=None):
+    """Number of key splits for decode attention, fixed for a batch size and a page-table width (it
+    must not depend on sequence lengths, which change under a captured graph; the table width is
+    the graph's own). While all blocks fit the GPU at once (two per SM with the three-deep rings):
+    as many splits as keep it so, up to ``max_splits``, and for long tables up to DECODE_MAX_SPLITS
+    while a split keeps 16 pages (one sequence of 32,768 tokens in 8 splits of its 8 kv heads kept
+    64 of 296 block slots busy: 0.55 of the copy peak for the step). Beyond that: enough for about
+    six waves of blocks, which evens out sequences of unequal lengths (measured at batch 64: 133 us
+    unsplit, 115 us in four splits)."""
     if resident_blocks is None:
         resident_blocks = 2 * sm_count()
     blocks = n_seq * n_kv_heads * ((group + 15) // 16)
     if blocks <= resident_blocks:
-        return max(1, min(max_splits, resident_blocks // blocks))
+        room = resident_blocks // blocks
+        return max(1, min(max_splits, room), min(DECODE_MAX_SPLITS, room, table_pages // 16))
     return max(1, min(max_splits, -(-6 * resident_blocks // blocks)))
 
 
@@ -286,8 +293,8 @@ def attention_decode_bf16(q, out, k_store, v_store, row_pos, page_table, n_heads
     _need(row_pos, "row_pos", torch.int32, 1), _need(page_table, "page_table", torch.int32, 2)
     _need(ws_acc, "ws_acc", torch.float32), _need(ws_ml, "ws_ml", torch.float32)
     n_seq = q.shape[0]
-    if not 1 <= nsplit <= 16:
-        raise KernelError(f"attention_decode_bf16: {nsplit} splits, the merge takes 1 to 16")
+    if not 1 <= nsplit <= DECODE_MAX_SPLITS:
+        raise KernelError(f"attention_decode_bf16: {nsplit} splits, the merge takes 1 to {DECODE_MAX_SPLITS}")
     if ws_acc is None or ws_ml is None or ws_acc.numel() < n_seq * n_heads * 4 * nsplit * head_dim \
             or ws_ml.numel() < n_seq * n_heads * 4 * nsplit * 2:
         raise KernelError("attention_decode_bf16: scratch too small for this batch and split count")

@@ -202,9 +202,9 @@ attn_decode_kernel(const bf16* q, float* ws_acc, float* ws_ml, const bf16* k_sto
     }
 }
 
-// grid (sequences * nh / 4), 128 threads: a warp merges the parts of one head (at most 64). Lane s
-// holds the (max, sum) of parts s and s + 32; the partial outputs of the first 16 parts are requested
-// together with them, so up to 16 parts cost one trip to memory after the wait.
+// grid (sequences * nh / 4), 128 threads: a warp merges the parts of one head (at most 128). Lane s
+// holds the (max, sum) of parts s, s + 32, s + 64 and s + 96; the partial outputs of the first 16
+// parts are requested together with them, so up to 16 parts cost one trip to memory after the wait.
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int parts, int n_heads) {
     pdl_launch_dependents();   // before the wait: see pdl_launch_dependents
@@ -215,8 +215,10 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int part
     const float2* ml = reinterpret_cast<const float2*>(ws_ml) + head * parts;
     const float* wa = ws_acc + head * parts * HD;
     const float2 none = make_float2(-INFINITY, 0.f);
-    const float2 p0 = lane < parts ? ml[lane] : none, p1 = lane + 32 < parts ? ml[lane + 32] : none;
-    float f0 = 0.f, f1 = 0.f, inv = 0.f;
+    float2 pm[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) pm[k] = lane + 32 * k < parts ? ml[lane + 32 * k] : none;
+    float fw[4] = {0.f, 0.f, 0.f, 0.f}, inv = 0.f;
     for (int base = 0; base < HD; base += 128) {
         const int d0 = base + lane * 4;
         const bool ok = d0 < HD;
@@ -228,17 +230,20 @@ attn_combine_kernel(const float* ws_acc, const float* ws_ml, bf16* out, int part
                 v[u] = ok && s0 + u < parts ? *reinterpret_cast<const float4*>(wa + (size_t)(s0 + u) * HD + d0)
                                             : make_float4(0.f, 0.f, 0.f, 0.f);
             if (base == 0 && s0 == 0) {       // the weights of the parts, once
-                float M = fmaxf(p0.x, p1.x);
+                float M = fmaxf(fmaxf(pm[0].x, pm[1].x), fmaxf(pm[2].x, pm[3].x));
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
-                f0 = M == -INFINITY ? 0.f : exp2f(p0.x - M);
-                f1 = M == -INFINITY ? 0.f : exp2f(p1.x - M);
-                float L = p0.y * f0 + p1.y * f1;
+                float L = 0.f;
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    fw[k] = M == -INFINITY ? 0.f : exp2f(pm[k].x - M);
+                    L += pm[k].y * fw[k];
+                }
 #pragma unroll
                 for (int d = 16; d >= 1; d >>= 1) L += __shfl_xor_sync(0xffffffffu, L, d);
                 inv = L > 0.f ? 1.f / L : 0.f;
             }
-            const float fsrc = s0 < 32 ? f0 : f1;   // a run of 16 parts lies in one half
+            const float fsrc = fw[s0 >> 5];         // a run of 16 parts lies in one group of 32
 #pragma unroll
             for (int u = 0; u < 16; u++) {
                 const float f = __shfl_sync(0xffffffffu, fsrc, (s0 + u) & 31);
@@ -291,11 +296,11 @@ DK_EXPORT int dk_attn_prefill_bf16(const void* q, void* out, const void* k_store
 }
 
 // ws_acc: n_seq * nh * 4 * nsplit * HD floats, ws_ml: n_seq * nh * 4 * nsplit * 2 floats: every warp of a
-// block leaves a partial result of its own, the merge kernel adds up the 4 * nsplit of a head (nsplit <= 16).
+// block leaves a partial result of its own, the merge kernel adds up the 4 * nsplit of a head (nsplit <= 32).
 DK_EXPORT int dk_attn_decode_bf16(const void* q, void* out, float* ws_acc, float* ws_ml, const void* k_store,
                                   const void* v_store, const int* row_pos, const int* page_table, int pt_stride,
                                   int n_seq, int nh, int nkv, int window, float scale, int nsplit, cudaStream_t st) {
-    if (nh % nkv != 0 || nsplit < 1 || nsplit > 16 || ws_acc == nullptr || ws_ml == nullptr) return (int)cudaErrorInvalidValue;
+    if (nh % nkv != 0 || nsplit < 1 || nsplit > 32 || ws_acc == nullptr || ws_ml == nullptr) return (int)cudaErrorInvalidValue;
     int e = ensure_smem_attr();
     if (e) return e;
     const int G = nh / nkv, mtiles = (G + 15) / 16;

@@ -145,7 +145,7 @@ class GQAAttention(Part):
         if dtype == torch.float32:
             api.attention_generic(q, o, kv.k, kv.v, ctx.row_pos, ctx.row_seq, table, nh, nkv, hd, window, s.scale)
         elif ctx.is_decode:
-            nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv)
+            nsplit = api.decode_splits(ctx.n_seq, nkv, nh // nkv, table.shape[1])
             ws_acc, ws_ml = ctx.scratch(("attn_decode", ctx.n_seq, nh, hd, nsplit),
                                         lambda: api.attention_decode_ws(ctx.n_seq, nh, hd, nsplit, dev))
             api.attention_decode_bf16(q, o, kv.k, kv.v, ctx.row_pos, table, nh, nkv, hd, window, s.scale, nsplit,

@@ -202,7 +202,8 @@ def test_attention_prefill_bf16(nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd,window,nsplit", [(4, 2, 16, 0, 1), (32, 8, 128, 0, 4), (6, 2, 48, 0, 8),
-                                                     (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 16)])
+                                                     (3, 1, 64, 90, 2), (20, 1, 32, 0, 4), (4, 4, 256, 0, 16), (8, 2, 128, 0, 32),
+                                                     (3, 1, 48, 0, 24)])
 def test_attention_decode_bf16(nh, nkv, hd, window, nsplit):
     before = [0, 63, 64, 300, 1000, 5]
     s = paged_setup(before, [1] * len(before), nkv, hd, torch.bfloat16, seed=15)

@@ -53,10 +53,17 @@ def test_decode_splits_depend_on_the_batch_only_and_stay_within_what_the_merge_t
     seen = {}
     for n_seq, nkv, group in itertools.product((1, 2, 8, 16, 32, 64, 128, 500), (1, 2, 8), (1, 4, 16, 20)):
         n = api.decode_splits(n_seq, nkv, group)
-        assert 1 <= n <= 16        # 4 partial results a split, and the merge takes 64
+        assert 1 <= n <= 8
+        for pages in (16, 64, 512, 4096):      # long page tables: more splits while the blocks still fit at once
+            wide = api.decode_splits(n_seq, nkv, group, pages)
+            assert n <= wide <= api.DECODE_MAX_SPLITS and (wide == n or wide * 16 <= pages)
+            blocks = n_seq * nkv * ((group + 15) // 16)
+            assert wide == n or blocks * wide <= 2 * api.sm_count()
         seen[(n_seq, nkv, group)] = n
     assert seen[(8, 8, 4)] == 4 and seen[(32, 8, 4)] == 1 and seen[(64, 8, 4)] == 4   # measured choices for the benchmark model
     assert seen[(1, 8, 4)] == 8
+    if api.sm_count() == 148:
+        assert api.decode_splits(1, 8, 4, 64) == 8 and api.decode_splits(1, 8, 4, 512) == 32 and api.decode_splits(8, 8, 4, 512) == 4
 
 
 def test_gemm_tc_fills_gpu_is_about_the_last_wave():
