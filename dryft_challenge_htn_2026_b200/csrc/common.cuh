@@ -56,13 +56,14 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // The kernel after this one may be launched once every block of this one has called this (or has
 // left). Most kernels call it after their wait, so at most one kernel runs ahead. The short kernels
-// that stand directly before a weight-streaming product of a decode step (the norms, the merge of
-// the attention parts, the embedding) call it before their wait: the product's blocks then come in
-// as soon as the SMs have room and fill their rings with weights while the kernel before the short
-// one is still at work. That is safe because every kernel waits before it reads or writes anything
-// that another kernel of the step writes (a wait returns only when the kernel before has finished,
-// which in turn has waited for the one before it), and what a product does before its wait reads
-// weights only.
+// that stand directly before a streaming kernel of a decode step (the norms, the merge of the
+// attention parts and the embedding before a product; the rotation before decode attention) call
+// it before their wait: the streaming kernel's blocks then come in as soon as the SMs have room
+// and fill their rings while the kernel before the short one is still at work. That is safe
+// because every kernel waits before it reads or writes anything that another kernel of the step
+// writes (a wait returns only when the kernel before has finished, which in turn has waited for
+// the one before it), and what a streaming kernel does before its wait reads only what no kernel
+// of the step writes: weights; positions, page ids and the cache pages of older tokens.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
 // Cache policy for what a decode step reads exactly once (weights, the keys and values of a sequence):

@@ -210,8 +210,8 @@ __global__ void qk_norm_rope_write_kernel(const T* qkv, const float* parts, int 
         w1[i] = on && nw ? nw[d] : 1.f;
         w2[i] = on && nw ? nw[d + half] : 1.f;
     }
-    pdl_wait();
-    pdl_launch_dependents();
+    pdl_launch_dependents();   // before the wait (see pdl_launch_dependents): what decode attention does before its own wait
+    pdl_wait();                // reads positions, page ids and cache pages of older tokens, none of them written in this step
     if (!work) return;
     const size_t x_off = (size_t)t * heads * hd + (size_t)hidx * hd;
     float x1[4] = {0.f, 0.f, 0.f, 0.f}, x2[4] = {0.f, 0.f, 0.f, 0.f};
