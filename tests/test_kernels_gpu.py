@@ -529,3 +529,31 @@ def test_gemm_tc_on_a_decode_step_of_17_to_128_rows(M, N, K):
         api.gemm_tc_check()
     finally:
         api.set_pdl(False)
+
+
+def test_gemm_tc_decode_form_at_random_shapes_and_plans():
+    """Forty random shapes (17 to 128 rows, widths and inner sizes that are multiples of 8 only, widths
+    below one tile) with random tile heights and slice counts: plain and gated epilogues, partial sums."""
+    rs = np.random.RandomState(123)
+    api.set_pdl(True)
+    try:
+        for case in range(40):
+            M = int(rs.randint(17, 129))
+            N = int(rs.choice([8, 24, 100, 136, 300, 1000, 1002, 2560])) if case % 2 else int(rs.randint(1, 200)) * 8
+            K = int(rs.randint(8, 400)) * 8
+            bn = int(rs.choice(api.TC_TILE_HEIGHTS))
+            kb = (K + 63) // 64
+            sk = int(rs.randint(1, 9))
+            while sk > 1 and (sk - 1) * ((kb + sk - 1) // sk) >= kb:
+                sk -= 1
+            x = rnd(M, K, dtype=torch.bfloat16, seed=1000 + case)
+            w = rnd(2 * N, K, dtype=torch.bfloat16, seed=2000 + case, scale=K ** -0.5)
+            ref = x.float() @ w.float().t()
+            r = api.gemm_tc(x, w[:N].contiguous(), api.MODE_STORE, None, (bn, sk))
+            close(r.sum() if sk > 1 else r, ref[:, :N], torch.bfloat16, f"case {case}: rows {M} width {N} inner {K} plan {(bn, sk)}")
+            g, u = ref[:, :N], ref[:, N:]
+            close(api.gemm_tc(x, w, api.MODE_SILU, None, (bn, 1)), g / (1 + torch.exp(-g)) * u, torch.bfloat16,
+                  f"case {case} gated: rows {M} width {N} inner {K} tile {bn}")
+        api.gemm_tc_check()
+    finally:
+        api.set_pdl(False)
