@@ -540,20 +540,19 @@ def skinny_tc_plan(M, N, K, mode, allow_partial=False):
 
 
 def gated_tc_plan(M, N):
-    """Weight rows per tile for the gated product of a prefill step (gemm_tc, MODE_SILU; N outputs):
-    the height whose tiles leave the last wave of blocks least empty, weighted by what a smaller
-    tile costs (its x tile is re-read for fewer outputs). At 2,048 rows and more every height fills
-    its waves and the largest wins; at 512 rows of the benchmark model 256-row tiles fill 2.05 waves
-    (a third wave for 8 tiles), 192-row tiles 2.76."""
+    """Weight rows per tile for the gated product of a prefill step (gemm_tc, MODE_SILU; N outputs).
+    One persistent block an SM works through the tiles in waves, and a step takes waves x what a
+    wave of that tile costs. Measured at 512 to 8,192 rows of three model sizes: a wave of 192-row
+    tiles costs 0.86 of a wave of 256-row tiles, and lower tiles no less than that (their share of
+    the rows of x per output grows), so the choice is between those two: 512 rows of the benchmark
+    model are 304 tiles of 256 (3 waves) or 408 of 192 (3 waves at 0.86)."""
     sms = sm_count()
     m_tiles = (M + 127) // 128
-    best = None
-    for bn, worth in ((256, 1.0), (192, 0.95), (160, 0.9), (144, 0.88), (128, 0.85)):
+
+    def cost(bn, wave):
         tiles = m_tiles * ((N + bn // 2 - 1) // (bn // 2))
-        score = worth * tiles / (-(-tiles // sms) * sms)
-        if best is None or score > best[0] + 1e-9:
-            best = (score, bn)
-    return best[1], 1
+        return -(-tiles // sms) * wave
+    return (192 if cost(192, 0.86) < cost(256, 1.0) else 256), 1
 
 
 def gemm_tc_fills_gpu(M, N, min_fill=0.8):
