@@ -5,7 +5,8 @@
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at the default batch of 8: K decode
 steps of the generation loop's own decode state (CUDA-graph replay), timed with CUDA events after W
-warm-up steps, every sequence at the midpoint of the size's workload: for ``4b`` a 2,048-token
+warm-up steps (at least 32 untimed steps in both arms, see MIN_UNTIMED_STEPS; the count is named in
+``config.untimed_steps``), every sequence at the midpoint of the size's workload: for ``4b`` a 2,048-token
 prompt (ragged 1,024..2,048 above batch 1) plus 1,024 tokens decoded so far of a 4,096-token
 context; ``8b`` 1,024 + 512 of 1,024; ``14b`` 2,048 + 256 of 512. ``e2e`` is the same measured
 through ``Engine.generate`` (host token lists in, host tokens out). ``prefill`` is one 2,048-token
@@ -138,8 +139,15 @@ def prefill_flops(cfg, tokens):
 
 
 # ------------------------------------------------------------------------------------ this library
+# Untimed steps before the timed ones: the W asked for, and at least this many, in both arms (after a
+# prefill under the power cap the SM clock needs some tens of steps to settle; with five untimed steps
+# the same step measured 5 % slower than with fifty). The count used is named in config.untimed_steps.
+MIN_UNTIMED_STEPS = 32
+
+
 def time_decode(torch, dk, model, cfg, size, batch, steps, warmup, seed):
-    """K decode steps of the generation loop's own decode state (graph replay), timed on the device."""
+    """K decode steps of the generation loop's own decode state (graph replay), timed on the device
+    after ``warmup`` untimed ones."""
     from dryft_challenge_htn_2026_b200.csrc import api
     from dryft_challenge_htn_2026_b200.engine.generate import GpuBackend
     from dryft_challenge_htn_2026_b200.sampling import SamplingParams
@@ -201,24 +209,20 @@ def time_prefill(torch, dk, model, cfg, tokens, iters=3):
     return statistics.median(times), prefill_flops(cfg, tokens)
 
 
-def time_e2e(torch, dk, model, size, batch, steps, seed):
-    """Decode tokens per second through Engine.generate: host lists in, host tokens out, from the
-    first yielded step (end of prefill) to the last."""
+def time_e2e(torch, dk, model, size, batch, steps, warmup, seed):
+    """Decode tokens per second through Engine.generate: host lists in, host tokens out; wall clock at
+    each yield, the timed steps those between yield number ``warmup`` and yield ``warmup + steps`` of
+    one call (what the reference arm's number is, see ref_decode)."""
     lens = prompt_lengths(size, batch, seed)
     prompts = random_prompts(model.spec.vocab_size, lens, seed)
     eng = dk.Engine(model=model)
     list(eng.generate(prompts, 4))          # first call: allocations and the graph of this batch shape (kept by the engine)
-    t_first = None
-    n = 0
-    for row in eng.generate(prompts, steps + 1):
-        if t_first is None:
-            t_first = time.perf_counter()
-        n += 1
-    t_last = time.perf_counter()
-    h2d = sum(len(p) for p in prompts) * 3 * 4 / (steps + 1)              # token ids, row->sequence, positions, once
+    stamps = [time.perf_counter() for _ in eng.generate(prompts, warmup + steps + 1)]
+    assert len(stamps) == warmup + steps + 1
+    h2d = sum(len(p) for p in prompts) * 3 * 4 / (warmup + steps + 1)     # token ids, row->sequence, positions, once
     del eng
     torch.cuda.empty_cache()
-    return batch * (n - 1) / (t_last - t_first), h2d, 4 * batch
+    return batch * steps / (stamps[warmup + steps] - stamps[warmup]), h2d, 4 * batch
 
 
 def point(run, pk):
@@ -263,13 +267,14 @@ def run_ours(args):
                                       "ms": round(ms, 3), "layers": cfg.num_hidden_layers,
                                       "frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}}))
         return 0
-    main_run = time_decode(torch, dk, model, cfg_d, size, args.batch, args.steps, warmup, seed=0)
-    e2e_val, h2d, d2h = time_e2e(torch, dk, model, size, args.batch, args.steps, seed=0)
+    untimed = max(warmup, MIN_UNTIMED_STEPS)
+    main_run = time_decode(torch, dk, model, cfg_d, size, args.batch, args.steps, untimed, seed=0)
+    e2e_val, h2d, d2h = time_e2e(torch, dk, model, size, args.batch, args.steps, untimed, seed=0)
     points, detail, prefill = {}, {}, None
     if not args.no_points:
         for b in SIZES[size]["batches"]:
             if b != args.batch:
-                detail[f"decode_b{b}"] = point(time_decode(torch, dk, model, cfg_d, size, b, max(64, args.steps), warmup, seed=b), pk)
+                detail[f"decode_b{b}"] = point(time_decode(torch, dk, model, cfg_d, size, b, max(64, args.steps), untimed, seed=b), pk)
                 points[f"decode_b{b}"] = detail[f"decode_b{b}"]["value"]
         ms, flops = time_prefill(torch, dk, model, cfg_d, PREFILL_TOKENS)
         prefill = {"value": round(PREFILL_TOKENS / ms * 1e3, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
@@ -282,7 +287,7 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: random weights N(0,0.02), uniform random token ids",
         "config": config_record(size, cfg_d, full_layers, args.batch, pk, ctx_mean_timed=round(main_run["ctx_mean"]),
-                                pdl=bool(args.pdl)),
+                                pdl=bool(args.pdl), untimed_steps=untimed),
         "clocks": main_run["clocks"],
         "e2e": {"value": round(e2e_val, 1), "unit": "tok/s", "h2d_bytes_per_step": round(h2d), "d2h_bytes_per_step": d2h},
         "gpu_launches": main_run["launches"] * args.steps,
@@ -392,6 +397,7 @@ def run_reference(args):
             cfg["num_hidden_layers"] = args.layers
         pk = peaks()
         warmup = max(3, args.warmup)
+        untimed = max(warmup, MIN_UNTIMED_STEPS)
         folder = tempfile.mkdtemp(prefix="dryft_ref_model_")
         try:
             t0 = time.time()
@@ -411,8 +417,8 @@ def run_reference(args):
             lens = prompt_lengths(size, batch, seed)
             if equal:
                 lens = [max(lens)] * batch
-            ms, c = ref_decode(torch, eng, random_prompts(V, lens, seed), steps, warmup, clocks)
-            ctx_mean = sum(lens) / batch + warmup + steps / 2
+            ms, c = ref_decode(torch, eng, random_prompts(V, lens, seed), steps, untimed, clocks)
+            ctx_mean = sum(lens) / batch + untimed + steps / 2
             nbytes = weight_bytes(cfg) + batch * ctx_mean * kv_bytes_per_token(cfg)
             return dict(ms=ms, tok_s=batch / ms * 1e3, bytes=nbytes, ctx_mean=ctx_mean, clocks=c)
 
@@ -454,14 +460,14 @@ def run_reference(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic: random weights N(0,0.02), uniform random token ids",
             "config": config_record(size, cfg, full_layers, args.batch, pk, ctx_mean_timed=round(main_run["ctx_mean"]),
-                                    reference_backend=backend,
+                                    reference_backend=f"{backend}, {len(set(lens))} streams",
                                     reference_env=" ".join(f"{k}={os.environ[k]}" for k in sorted(REF_ENV)),
-                                    streams=len(set(lens))),
+                                    untimed_steps=untimed),
             "clocks": main_run["clocks"],
             # the reference's only interface is the host-side generator: host token lists in, host tokens out;
             # value and e2e are the same measurement (wall clock between yields)
             "e2e": {"value": round(main_run["tok_s"], 1), "unit": "tok/s",
-                    "h2d_bytes_per_step": round(sum(lens) * 8 / (warmup + args.steps + 1)), "d2h_bytes_per_step": 8 * args.batch},
+                    "h2d_bytes_per_step": round(sum(lens) * 8 / (untimed + args.steps + 1)), "d2h_bytes_per_step": 8 * args.batch},
             "gpu_launches": None,
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / pk["hbm_gbs"], 4)},
